@@ -1,0 +1,145 @@
+/*
+ * q4b200 — C ABI of the B200 (sm_100a) block_q4_0 INT4 matmul library.
+ *
+ * This is the boundary a host binding loads instead of metalcore's pybind11 extension
+ * `metalcore_backend` (packages/metalcore/src/metalcore/native/core_mps.mm:6866-6952) for
+ * the q4_0 path.  Plain pointers and sizes only; every pointer is a DEVICE pointer unless the
+ * name says host.  All calls are asynchronous on the given stream (a cudaStream_t passed as
+ * void*; NULL = the legacy default stream), never synchronise, never allocate device memory
+ * and return 0 or a q4b_status code.  The device used is the calling thread's current device.
+ *
+ * Tensor layouts
+ *   blocks     uint8 [K/32, N, 18]  interchange format, bit-exact with the reference's
+ *              quantize_ggml_q4_0 (quantization.py:307-371): fp16 scale d (little endian),
+ *              then 16 bytes, byte j = q[2j] | q[2j+1] << 4.
+ *   prepacked  uint8 [ceil(K/64), ceil(N/16), 576]  internal streaming format, one 576-byte
+ *              tile per 16 output columns x 64 k.  Same information as `blocks` (18 bytes per
+ *              32 weights), rearranged so that a warp reads a tile with one 128-bit load per
+ *              lane plus one 64-bit load of scales.  q4b_prepacked_bytes gives its size; the
+ *              buffer must be 16-byte aligned.  Tile layout:
+ *                bytes [0,512): 32 slots of 16 bytes; slot p = c*8 + g (g = p%8 column-in-
+ *                  octet, c = p/8 k-octet) holds four 32-bit words: blocks (kb0,g),(kb0,g+8),
+ *                  (kb0+1,g),(kb0+1,g+8), each word = the 8 nibbles q[8c..8c+7] of that block
+ *                  stored as q0|q2<<4|q4<<8|q6<<12|q1<<16|q3<<20|q5<<24|q7<<28;
+ *                bytes [512,576): 8 rows g of four fp16 scales d(kb0,g), d(kb0,g+8),
+ *                  d(kb0+1,g), d(kb0+1,g+8).
+ *              Padding blocks (k >= K or n >= N) have d = 0 and q = 8.
+ */
+#ifndef Q4B200_H
+#define Q4B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define Q4B_API __attribute__((visibility("default")))
+#else
+#define Q4B_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    Q4B_OK = 0,
+    Q4B_ERR_ARG = 1,      /* null pointer, negative size, unknown enum value            */
+    Q4B_ERR_SHAPE = 2,    /* K not a multiple of 32, size beyond the supported range    */
+    Q4B_ERR_DTYPE = 3,    /* dtype not supported by this entry point                    */
+    Q4B_ERR_ALIGN = 4,    /* pointer or leading dimension not aligned as documented     */
+    Q4B_ERR_ARCH = 5,     /* current device is not compute capability 10.x              */
+    Q4B_ERR_CUDA = 6,     /* a CUDA runtime call failed; see q4b_last_cuda_error        */
+    Q4B_ERR_TIMEOUT = 7,  /* a bounded device-side wait gave up (read via q4b_gemm_status) */
+    Q4B_ERR_TOO_LARGE = 8 /* problem exceeds a fixed internal buffer                    */
+} q4b_status;
+
+typedef enum { Q4B_F32 = 0, Q4B_F16 = 1, Q4B_BF16 = 2 } q4b_dtype;
+
+/* layout of the floating-point weight given to q4b_quantize */
+typedef enum {
+    Q4B_LAYOUT_KN = 0,    /* [K, N], N contiguous: the reference's quantize_ggml_q4_0 input */
+    Q4B_LAYOUT_NK = 1     /* [N, K], K contiguous: torch.nn.Linear.weight as stored         */
+} q4b_layout;
+
+/* flags for the matmul entry points */
+enum {
+    Q4B_FLAG_NONE = 0,
+    /* Launch with programmatic dependent launch: the kernel may start fetching WEIGHTS while
+     * earlier work on the stream is still running, and waits for that work before it reads x
+     * or writes y.  Only valid when nothing still in flight on the stream writes `prepacked`. */
+    Q4B_FLAG_PDL = 1
+};
+
+Q4B_API const char *q4b_strerror(int status);
+/* text of the last CUDA runtime error seen by this thread inside the library ("" if none) */
+Q4B_API const char *q4b_last_cuda_error(void);
+Q4B_API int q4b_version(void);
+/* Q4B_OK when the current device can run the kernels (compute capability 10.x) */
+Q4B_API int q4b_device_ok(void);
+
+/* bytes of the prepacked buffer for a [K, N] weight; 0 if K is not a multiple of 32 */
+Q4B_API size_t q4b_prepacked_bytes(int64_t K, int64_t N);
+
+/*
+ * Quantize + pack.  Replaces the torch pipeline of quantize_ggml_q4_0
+ * (quantization.py:307-371; the reference has no native kernel for it).  `w` is [K, N] or
+ * [N, K] per `layout`, dense (leading dimension = inner extent), dtype f32 / f16 / bf16; the
+ * arithmetic rounds after every step in that dtype exactly as the reference's torch ops do,
+ * so `blocks_out` is bit-identical to the reference.  Either output may be NULL.
+ */
+Q4B_API int q4b_quantize(const void *w, int w_dtype, int64_t K, int64_t N, int layout,
+                 void *blocks_out, void *prepacked_out, void *stream);
+
+/* interchange blocks -> prepacked tiles, and back (both exact, no arithmetic) */
+Q4B_API int q4b_repack(const void *blocks, int64_t K, int64_t N, void *prepacked_out, void *stream);
+Q4B_API int q4b_unpack(const void *prepacked, int64_t K, int64_t N, void *blocks_out, void *stream);
+
+/*
+ * blocks -> dense W [K, N] of out_dtype: W = (q - 8) * float(d) in fp32, then cast.
+ * Replaces dequantize_ggml_q4_0 (quantization.py:374-419).
+ */
+Q4B_API int q4b_dequantize(const void *blocks, int64_t K, int64_t N, void *w_out, int out_dtype,
+                   void *stream);
+
+/*
+ * Y[M, N] = X[M, K] . dequant(W), fp32 accumulation, Y of the same dtype as X (f16 or bf16).
+ * Replaces matmul_ggml_q4_0_metal (core_mps.mm:5917-5975) and the Metal kernel
+ * matmul_ggml_q4_0 (quant_kernels.metal:1738-1886).  X rows are K contiguous elements with
+ * leading dimension ldx (elements, multiple of 8, X 16-byte aligned); Y has leading
+ * dimension ldy (elements).
+ *
+ *   q4b_gemv   decode path, 1 <= M <= 16: streams the prepacked tiles once with 128-bit
+ *              loads, dequantises in registers, warp-level mma + split-K reduction in the CTA.
+ *   q4b_gemm   prefill path, any M >= 1 (intended for M >= 17): TMA -> shared memory ->
+ *              dequantise to bf16/fp16 -> tcgen05.mma with TMEM accumulators.
+ *              Needs K % 64 == 0, ldx % 8 == 0, ldy % 8 == 0 and 16-byte aligned X and Y.
+ *   q4b_matmul picks q4b_gemv for M <= 16, otherwise q4b_gemm.
+ */
+Q4B_API int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+             int64_t K, int64_t N, void *y, int64_t ldy, int flags, void *stream);
+Q4B_API int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+             int64_t K, int64_t N, void *y, int64_t ldy, int flags, void *stream);
+Q4B_API int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+               int64_t K, int64_t N, void *y, int64_t ldy, int flags, void *stream);
+
+/*
+ * The tcgen05 kernel bounds every mbarrier wait; a wait that gives up makes the kernel set a
+ * word in a small per-device status buffer and return early.  This call synchronises the
+ * stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with *detail (may be
+ * NULL) = which wait gave up.  It never traps or faults the device.
+ */
+Q4B_API int q4b_gemm_status(void *stream, int *detail);
+
+/*
+ * Host-buffer convenience used for end-to-end timing: x_host and y_host are (ideally pinned)
+ * HOST pointers; x_dev / y_dev are caller-provided device staging buffers of M*K and M*N
+ * elements.  Enqueues H2D copy of X, q4b_matmul, D2H copy of Y on `stream`.
+ */
+Q4B_API int q4b_matmul_host(const void *x_host, void *x_dev, int x_dtype, int64_t M,
+                    const void *prepacked, int64_t K, int64_t N, void *y_dev, void *y_host,
+                    int flags, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4B200_H */

@@ -1,0 +1,44 @@
+"""metalops_b200 — B200-native (sm_100a) implementation of metalcore's block_q4_0 INT4 matmul path.
+
+Exports the hot-path names of the reference package (``packages/metalcore/src/metalcore/
+__init__.py:38-39,174-184``) with the same signatures.  All compute runs in hand-written CUDA
+kernels behind the C ABI of ``include/q4b200.h``; importing this package loads that library and
+raises if it has not been built (``python -m metalops_b200.build``).
+"""
+from . import _cabi
+
+_cabi.load()  # fail loudly at import time when the CUDA library is missing
+
+from .quantization import (  # noqa: E402
+    BLOCK_Q4_0_SIZE,
+    QK4_0,
+    Int4Linear,
+    Q4Prepacked,
+    dequantize_ggml_q4_0,
+    dequantize_int4,
+    matmul_ggml_q4_0,
+    matmul_int4,
+    matmul_int8,
+    prepack_ggml_q4_0,
+    quantize_ggml_q4_0,
+    quantize_int4,
+    unpack_ggml_q4_0,
+)
+from .sharding import ColumnParallelQ4Linear, shard_bounds  # noqa: E402
+
+__version__ = "0.1.0"
+
+
+def has_native_kernels() -> bool:
+    """True when the current CUDA device can run the kernels (compute capability 10.x)."""
+    import torch
+
+    return torch.cuda.is_available() and _cabi.load().q4b_device_ok() == _cabi.OK
+
+
+__all__ = [
+    "quantize_ggml_q4_0", "dequantize_ggml_q4_0", "matmul_ggml_q4_0", "prepack_ggml_q4_0",
+    "unpack_ggml_q4_0", "Q4Prepacked", "Int4Linear", "quantize_int4", "dequantize_int4", "matmul_int4",
+    "matmul_int8", "ColumnParallelQ4Linear", "shard_bounds", "has_native_kernels", "QK4_0",
+    "BLOCK_Q4_0_SIZE",
+]

@@ -1,0 +1,90 @@
+"""ctypes binding of ``libq4b200.so`` (declared in ``include/q4b200.h``).
+
+The library is the only compute path of this package.  If it is missing or fails to load the
+import raises; there is no fallback of any kind.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libq4b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+LAYOUT_KN, LAYOUT_NK = 0, 1
+FLAG_NONE, FLAG_PDL = 0, 1
+OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_ARCH, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(9)
+
+DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+_i64, _vp, _ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+
+# every symbol include/q4b200.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "q4b_strerror": (ctypes.c_char_p, [_ci]),
+    "q4b_last_cuda_error": (ctypes.c_char_p, []),
+    "q4b_version": (_ci, []),
+    "q4b_device_ok": (_ci, []),
+    "q4b_prepacked_bytes": (ctypes.c_size_t, [_i64, _i64]),
+    "q4b_quantize": (_ci, [_vp, _ci, _i64, _i64, _ci, _vp, _vp, _vp]),
+    "q4b_repack": (_ci, [_vp, _i64, _i64, _vp, _vp]),
+    "q4b_unpack": (_ci, [_vp, _i64, _i64, _vp, _vp]),
+    "q4b_dequantize": (_ci, [_vp, _i64, _i64, _vp, _ci, _vp]),
+    "q4b_gemv": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
+    "q4b_gemm": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
+    "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
+    "q4b_gemm_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
+    "q4b_matmul_host": (_ci, [_vp, _vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp, _ci, _vp]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and set the prototypes.  Raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m metalops_b200.build` "
+                "(needs nvcc). This package has no CPU or PyTorch fallback.")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)          # AttributeError if the library lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    """Turn a non-zero status into the RuntimeError the reference's TORCH_CHECKs would raise
+    (core_mps.mm:5923-5938), with the library's own message."""
+    if status != OK:
+        lib = load()
+        msg = lib.q4b_strerror(status).decode()
+        if status == ERR_CUDA:
+            msg += ": " + lib.q4b_last_cuda_error().decode()
+        raise RuntimeError(f"{what}: {msg}")
+
+
+def require_device(t: torch.Tensor, name: str) -> None:
+    if t.device.type != "cuda":
+        raise RuntimeError(
+            f"{name} must be a CUDA tensor (got {t.device}); this build is B200-only and has no CPU fallback")
+
+
+_checked_devices: set[int] = set()
+
+
+def stream_ptr(device: torch.device) -> int:
+    """Current torch stream of ``device`` as a raw cudaStream_t; checks the architecture once."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _checked_devices:
+        with torch.cuda.device(idx):
+            check(load().q4b_device_ok(), "q4b200")
+        _checked_devices.add(idx)
+    return torch.cuda.current_stream(idx).cuda_stream

@@ -1,0 +1,112 @@
+// C-ABI glue: status strings, device checks, the M-based dispatcher and the host-buffer
+// convenience entry.  The kernels live in q4b_quantize.cu, q4b_gemv.cu and q4b_gemm_sm100.cu.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "q4b_common.cuh"
+
+namespace q4b {
+
+static thread_local char g_cuda_err[256] = "";
+
+void set_cuda_error(cudaError_t e) {
+    const char *name = cudaGetErrorName(e);
+    const char *text = cudaGetErrorString(e);
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", name ? name : "?", text ? text : "?");
+    // configuration errors are sticky in cudaGetLastError only; clear so the next launch is clean
+    (void)cudaGetLastError();
+}
+
+// Per-device facts, read once.  Guarded by a mutex: callers may use several host threads.
+struct DevInfo {
+    bool known = false;
+    int sms = 0;
+    int major = 0;
+};
+static DevInfo g_dev[64];
+static std::mutex g_dev_mu;
+
+static const DevInfo *dev_info() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    DevInfo &d = g_dev[dev];
+    if (!d.known) {
+        if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+        if (cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
+        d.known = true;
+    }
+    return &d;
+}
+
+int device_sm_count() {
+    const DevInfo *d = dev_info();
+    return d ? d->sms : 148;
+}
+
+// Q4B_GEMV_KSPLIT=1|2|4|8 forces the decode kernel's k-split (benchmark sweeps only).
+int gemv_ksplit_override() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("Q4B_GEMV_KSPLIT");
+        int k = e ? atoi(e) : 0;
+        v = (k == 1 || k == 2 || k == 4 || k == 8) ? k : 0;
+    }
+    return v;
+}
+
+}  // namespace q4b
+
+using namespace q4b;
+
+extern "C" const char *q4b_strerror(int status) {
+    switch (status) {
+        case Q4B_OK: return "ok";
+        case Q4B_ERR_ARG: return "invalid argument (null pointer, non-positive size or unknown enum)";
+        case Q4B_ERR_SHAPE: return "unsupported shape (K must be a multiple of 32; see the entry point's limits)";
+        case Q4B_ERR_DTYPE: return "unsupported dtype for this entry point";
+        case Q4B_ERR_ALIGN: return "pointer or leading dimension is not aligned as the entry point requires";
+        case Q4B_ERR_ARCH: return "the current device is not compute capability 10.x (B200, sm_100a)";
+        case Q4B_ERR_CUDA: return "a CUDA runtime call failed (see q4b_last_cuda_error)";
+        case Q4B_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case Q4B_ERR_TOO_LARGE: return "problem exceeds a fixed internal buffer";
+        default: return "unknown q4b status";
+    }
+}
+
+extern "C" const char *q4b_last_cuda_error(void) { return g_cuda_err; }
+
+extern "C" int q4b_version(void) { return 100; }
+
+extern "C" int q4b_device_ok(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        (void)cudaGetLastError();
+        return Q4B_ERR_ARCH;
+    }
+    const DevInfo *d = dev_info();
+    if (d == nullptr) return Q4B_ERR_CUDA;
+    return d->major == 10 ? Q4B_OK : Q4B_ERR_ARCH;
+}
+
+extern "C" int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                          int64_t N, void *y, int64_t ldy, int flags, void *stream) {
+    if (M >= 1 && M <= 16) return q4b_gemv(x, x_dtype, M, ldx, prepacked, K, N, y, ldy, flags, stream);
+    return q4b_gemm(x, x_dtype, M, ldx, prepacked, K, N, y, ldy, flags, stream);
+}
+
+extern "C" int q4b_matmul_host(const void *x_host, void *x_dev, int x_dtype, int64_t M, const void *prepacked,
+                               int64_t K, int64_t N, void *y_dev, void *y_host, int flags, void *stream) {
+    if (x_host == nullptr || x_dev == nullptr || y_dev == nullptr || y_host == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || K <= 0 || N <= 0) return Q4B_ERR_ARG;
+    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    Q4B_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, st));
+    // the copy above writes x, so the kernel must not start before it: no early launch here
+    int rc = q4b_matmul(x_dev, x_dtype, M, K, prepacked, K, N, y_dev, N, flags & ~Q4B_FLAG_PDL, stream);
+    if (rc != Q4B_OK) return rc;
+    Q4B_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, (size_t)M * N * 2, cudaMemcpyDeviceToHost, st));
+    return Q4B_OK;
+}

@@ -1,0 +1,430 @@
+// Prefill path: Y[M, N] = X[M, K] . dequant(W) on the 5th-generation tensor cores.
+//
+// Replaces the reference's 64x32-tile simdgroup kernel matmul_ggml_q4_0
+// (packages/metalcore/src/metalcore/native/quant_kernels.metal:1738-1886, launched by
+// core_mps.mm:5917-5975) for M above the decode range.
+//
+// One persistent CTA per SM, tile 128 (M) x 256 (N) x 64 (K) per pipeline stage:
+//   warp 0      producer: TMA tile load of X (128 x 64, 128-byte swizzle) and one bulk copy of
+//               the stage's packed weights (16 prepacked tiles = 9216 contiguous bytes)
+//   warps 6-13  dequantise the packed stage into the K-major, 128-byte-swizzled bf16/fp16 B
+//               operand in shared memory ((q-8)*d, one rounding), then fence to the async proxy
+//   warp 1      one thread issues tcgen05.mma (kind::f16, M128 N256 K16) x 4 per stage,
+//               accumulating in TMEM; tcgen05.commit releases the stage / publishes the tile
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (double-buffered, 2 x 256 TMEM
+//               columns, so it overlaps the next tile's main loop), convert, 16-byte stores
+// Every mbarrier wait is bounded; a wait that gives up records a code in g_gemm_status, raises
+// a CTA-wide abort flag and every role leaves through the common exit that frees TMEM.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "q4b_common.cuh"
+
+namespace q4b {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 3;
+constexpr int A_BYTES = BM * BK * 2;                 // 16384
+constexpr int B_BYTES = BN * BK * 2;                 // 32768
+constexpr int W_TILES = BN / TILE_N;                 // 16 prepacked tiles per stage
+constexpr int W_BYTES = W_TILES * TILE_BYTES;        // 9216
+constexpr int NUM_DEQ_WARPS = 8;
+constexpr int FIRST_DEQ_WARP = 6;                   // warps 2..5 are the epilogue
+constexpr int THREADS = (FIRST_DEQ_WARP + NUM_DEQ_WARPS) * 32;   // 448
+constexpr int TMEM_COLS = 512;                       // two 256-column fp32 accumulators
+constexpr int SMEM_A = 0;
+constexpr int SMEM_B = SMEM_A + STAGES * A_BYTES;
+constexpr int SMEM_W = SMEM_B + STAGES * B_BYTES;
+constexpr int SMEM_BAR = SMEM_W + STAGES * W_BYTES;
+constexpr int NUM_BARS = 3 * STAGES + 4;
+constexpr int SMEM_USED = SMEM_BAR + NUM_BARS * 8 + 16;
+constexpr int SMEM_DYN = SMEM_USED + 1024;           // slack to align the base to 1024 bytes
+constexpr long long WAIT_LIMIT_CYCLES = 1LL << 28;   // ~0.15 s; far above any legitimate wait
+
+__device__ int g_gemm_status = 0;
+
+// ---- thin PTX wrappers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when another role aborted or when this wait itself ran out, in
+// which case it records `code` (first writer wins) and raises the CTA-wide abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(&g_gemm_status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes
+// (64 16-bit elements) with the 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);     // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                          // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: kind::f16, fp32 accumulate, A and B K-major, dense.
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, int m, int n) {
+    return (1u << 4)                              // D format f32
+           | ((bf16 ? 1u : 0u) << 7)              // A format
+           | ((bf16 ? 1u : 0u) << 10)             // B format
+           | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2_out(float a, float b) {
+    if constexpr (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+}
+// fp16 scale bits -> packed pair (d, d) in the operand dtype
+template <bool BF16> __device__ __forceinline__ uint32_t scale_pair(uint16_t dbits) {
+    if constexpr (BF16) {
+        __nv_bfloat16 b = __float2bfloat16_rn(__half2float(__ushort_as_half(dbits)));
+        uint32_t u = __bfloat16_as_ushort(b);
+        return u | (u << 16);
+    } else {
+        return (uint32_t)dbits | ((uint32_t)dbits << 16);
+    }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
+                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (base - raw);
+    const uint32_t bar0 = base + SMEM_BAR;
+    auto bar_full = [&](int s) { return bar0 + 8u * s; };                    // TMA bytes landed
+    auto bar_fullb = [&](int s) { return bar0 + 8u * (STAGES + s); };        // B operand dequantised
+    auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };    // MMAs of the stage retired
+    auto bar_tfull = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };    // accumulator complete
+    auto bar_tempty = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int *abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_fullb(s), NUM_DEQ_WARPS);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull(a), 1);
+            mbar_init(bar_tempty(a), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+
+    const int NT = (int)tiles_n(N);                    // prepacked 16-column tiles
+    const int num_mt = (M + BM - 1) / BM, num_nt = (N + BN - 1) / BN;
+    const int num_tiles = num_mt * num_nt;
+    const int k_stages = (K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                const int mt = t % num_mt, nt = t / num_mt;
+                const int nt0 = nt * W_TILES;
+                const int valid = min(W_TILES, NT - nt0);
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag, 1)) goto done;
+                    mbar_arrive_expect_tx(bar_full(stage), (uint32_t)(A_BYTES + valid * TILE_BYTES));
+                    tma_load_2d(base + SMEM_A + stage * A_BYTES, &tmap_x, ks * BK, mt * BM, bar_full(stage));
+                    bulk_load(base + SMEM_W + stage * W_BYTES, prepacked + ((size_t)ks * NT + nt0) * TILE_BYTES,
+                              (uint32_t)(valid * TILE_BYTES), bar_full(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BF16, BM, BN);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1, abort_flag, 2)) goto done;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!mbar_wait(bar_full(stage), phase, abort_flag, 3)) goto done;
+                    if (!mbar_wait(bar_fullb(stage), phase, abort_flag, 4)) goto done;
+                    tc_fence_after();
+                    const uint64_t adesc = make_kmajor_sw128_desc(base + SMEM_A + stage * A_BYTES);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + stage * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);   // +32 bytes per k16
+                    tc_commit(bar_empty(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                tc_commit(bar_tfull(acc));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else if (warp < FIRST_DEQ_WARP) {
+        // ---------------- epilogue ----------------
+        const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const int mt = t % num_mt, nt = t / num_mt;
+            if (!mbar_wait(bar_tfull(acc), acc_phase, abort_flag, 5)) goto done;
+            tc_fence_after();
+            const int m = mt * BM + quad * 32 + lane;
+            const int n_base = nt * BN;
+            uint16_t *yrow = y + (size_t)m * ldy;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                uint32_t r[32];
+                tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
+                tc_wait_ld();
+                const int n0 = n_base + ch * 32;
+                if (m < M && n0 < N) {
+                    if (vec_store && n0 + 32 <= N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = pack2_out<BF16>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack2_out<BF16>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack2_out<BF16>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack2_out<BF16>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            *reinterpret_cast<uint4 *>(yrow + n0 + 8 * v) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + j < N) yrow[n0 + j] = (uint16_t)(pack2_out<BF16>(__uint_as_float(r[j]), 0.0f) & 0xFFFF);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    } else {
+        // ---------------- dequantise: packed stage -> swizzled K-major B operand ----------------
+        const int dw = warp - FIRST_DEQ_WARP;
+        const int g = lane & 7, c = lane >> 3;           // a quarter-warp covers 8 rows of one k-octet
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const int nt = t / num_mt;
+            const int valid = min(W_TILES, NT - nt * W_TILES);
+            for (int ks = 0; ks < k_stages; ++ks) {
+                if (!mbar_wait(bar_full(stage), phase, abort_flag, 6)) goto done;
+                const uint8_t *wst = smem + SMEM_W + stage * W_BYTES;
+                uint8_t *bst = smem + SMEM_B + stage * B_BYTES;
+#pragma unroll
+                for (int i = 0; i < W_TILES / NUM_DEQ_WARPS; ++i) {
+                    const int tl = dw * (W_TILES / NUM_DEQ_WARPS) + i;
+                    if (tl < valid) {
+                        const uint4 qw = *reinterpret_cast<const uint4 *>(wst + tl * TILE_BYTES + (c * 8 + g) * 16);
+                        const uint2 dq = *reinterpret_cast<const uint2 *>(wst + tl * TILE_BYTES + TILE_QS_BYTES + g * 8);
+                        const uint32_t words[4] = {qw.x, qw.y, qw.z, qw.w};
+                        const uint16_t dbits[4] = {(uint16_t)(dq.x & 0xFFFF), (uint16_t)(dq.x >> 16),
+                                                   (uint16_t)(dq.y & 0xFFFF), (uint16_t)(dq.y >> 16)};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // word j: block (kb = j/2) of row g + 8*(j%2); 8 consecutive k = one 16-byte chunk
+                            const int row = tl * TILE_N + g + 8 * (j & 1);
+                            const int chunk = (j >> 1) * 4 + c;
+                            uint32_t h[4];
+                            dequant_word<BF16>(words[j], h);
+                            const uint32_t d2 = scale_pair<BF16>(dbits[j]);
+                            uint4 o;
+                            if constexpr (BF16) {
+                                o.x = bmul2_bits(h[0], d2); o.y = bmul2_bits(h[1], d2);
+                                o.z = bmul2_bits(h[2], d2); o.w = bmul2_bits(h[3], d2);
+                            } else {
+                                o.x = hmul2_bits(h[0], d2); o.y = hmul2_bits(h[1], d2);
+                                o.z = hmul2_bits(h[2], d2); o.w = hmul2_bits(h[3], d2);
+                            }
+                            *reinterpret_cast<uint4 *>(bst + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4)) = o;
+                        }
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_fullb(stage));
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    }
+
+done:
+    tc_fence_before();
+    __syncthreads();
+    if (s_abort) {
+        // give copies and MMAs still in flight time to land before shared memory and TMEM go away
+        for (int i = 0; i < 64; ++i) __nanosleep(20000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime, so the library has no link dependency on libcuda
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+template <bool BF16>
+static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M, int N, int K, int64_t ldy,
+                  int vec_store, int sms, cudaStream_t st) {
+    // per call: the attribute is per device and a process may drive several
+    Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sms ? tiles : sms;
+    gemm_tcgen05_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K,
+                                                             ldy, vec_store);
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+}  // namespace gemm
+
+int device_sm_count();
+
+}  // namespace q4b
+
+using namespace q4b;
+
+extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                        int64_t N, void *y, int64_t ldy, int flags, void *stream) {
+    (void)flags;
+    if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
+    if (K % QK || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return Q4B_ERR_SHAPE;
+    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
+    if (q4b_device_ok() != Q4B_OK) return Q4B_ERR_ARCH;
+    gemm::EncodeTiledFn enc = gemm::get_encode_fn();
+    if (enc == nullptr) return Q4B_ERR_CUDA;
+
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)gemm::BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&tmap, x_dtype == Q4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                     const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return Q4B_ERR_ARG;
+    const int vec_store = (aligned(y, 16) && ldy % 8 == 0) ? 1 : 0;
+    const int sms = device_sm_count();
+    cudaStream_t st = (cudaStream_t)stream;
+    return x_dtype == Q4B_BF16
+               ? gemm::launch<true>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st)
+               : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st);
+}
+
+extern "C" int q4b_gemm_status(void *stream, int *detail) {
+    Q4B_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    int h = 0;
+    Q4B_CUDA_TRY(cudaMemcpyFromSymbol(&h, gemm::g_gemm_status, sizeof(int)));
+    if (detail) *detail = h;
+    if (h != 0) {
+        const int zero = 0;
+        Q4B_CUDA_TRY(cudaMemcpyToSymbol(gemm::g_gemm_status, &zero, sizeof(int)));
+        return Q4B_ERR_TIMEOUT;
+    }
+    return Q4B_OK;
+}

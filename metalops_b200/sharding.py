@@ -1,0 +1,80 @@
+"""Column-parallel sharding of a q4_0 linear layer over the GPUs of one node.
+
+The reference is single-device; this is the multi-GPU form its q4_0 matmul takes here.  Every
+(k-block, n) quantization block is independent, so rank r of g owns the output columns
+``[r*N/g, (r+1)*N/g)``: it quantizes and keeps only that slice of the weight, X is replicated,
+and each rank computes ``Y_r [M, N/g]`` with no communication.  Only when the caller asks for
+the full ``[M, N]`` is there an exchange: one NCCL all-gather of the column shards over NVLink.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import quantization as Q
+
+
+def shard_bounds(N: int, world: int, rank: int, multiple: int = 16) -> Tuple[int, int]:
+    """Columns ``[n0, n1)`` owned by ``rank``.  N must split evenly into slices that are a
+    multiple of ``multiple`` columns (16 = one streaming tile), so every rank runs the same
+    shapes and the all-gather needs no padding."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    if N % world or (N // world) % multiple:
+        raise ValueError(f"N={N} does not split into {world} column shards of a multiple of {multiple}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def gather_columns(y_local: torch.Tensor, group=None, world: Optional[int] = None) -> torch.Tensor:
+    """All-gather column shards ``[M, N/g]`` into ``[M, N]`` (rank-major column order).
+
+    For M == 1 the gathered buffer already is ``[1, N]``; for M > 1 the collective lands as
+    ``[g, M, N/g]`` and is permuted locally."""
+    world = world if world is not None else dist.get_world_size(group)
+    if world == 1:
+        return y_local
+    M, n_local = y_local.shape
+    buf = torch.empty((world * M, n_local), dtype=y_local.dtype, device=y_local.device)   # rank-major rows
+    dist.all_gather_into_tensor(buf, y_local.contiguous(), group=group)
+    if M == 1:
+        return buf.view(1, world * n_local)
+    return buf.view(world, M, n_local).permute(1, 0, 2).reshape(M, world * n_local)
+
+
+class ColumnParallelQ4Linear(nn.Module):
+    """One rank's slice of a q4_0 linear layer, column-parallel over N.
+
+    ``from_float`` takes the FULL floating-point weight ``[K, N]`` (or an ``nn.Linear``), keeps
+    and quantizes only this rank's columns.  ``forward(x, gather_output=False)`` returns the
+    local ``[M, N/g]`` slice; with ``gather_output=True`` the full ``[M, N]``.
+
+    ``matmul`` is the local product; it defaults to the CUDA path and exists as a parameter so
+    the host-side sharding logic can be exercised on CPU ranks in tests.
+    """
+
+    def __init__(self, K: int, N: int, rank: int, world: int, group=None,
+                 matmul: Optional[Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = None):
+        super().__init__()
+        self.K, self.N, self.rank, self.world, self.group = K, N, rank, world, group
+        self.n0, self.n1 = shard_bounds(N, world, rank)
+        self._matmul = matmul or Q.matmul_ggml_q4_0
+        self.register_buffer("weight_blocks", torch.zeros((K // Q.QK4_0, self.n1 - self.n0, Q.BLOCK_Q4_0_SIZE),
+                                                          dtype=torch.uint8))
+        self._prepacked = None
+
+    @classmethod
+    def from_float(cls, weight_kn: torch.Tensor, rank: int, world: int, group=None, matmul=None,
+                   quantize: Optional[Callable[[torch.Tensor], torch.Tensor]] = None) -> "ColumnParallelQ4Linear":
+        K, N = weight_kn.shape
+        mod = cls(K, N, rank, world, group=group, matmul=matmul)
+        shard = weight_kn[:, mod.n0:mod.n1].contiguous()
+        mod.weight_blocks = (quantize or Q.quantize_ggml_q4_0)(shard)
+        return mod
+
+    def forward(self, x: torch.Tensor, gather_output: bool = False) -> torch.Tensor:
+        y = self._matmul(x, self.weight_blocks)
+        return gather_columns(y, self.group, self.world) if gather_output else y
