@@ -383,7 +383,7 @@ def bench_gemm(dev, stream, lib, peaks, traffic, args):
         detail = torch.zeros(1, dtype=torch.int32)
         import ctypes
         d = ctypes.c_int(0)
-        rc = lib.q4b_gemm_status(stream.cuda_stream, ctypes.byref(d))
+        rc = lib.q4b_wait_status(stream.cuda_stream, ctypes.byref(d))
         if rc:
             return {"error": f"gemm status {rc} detail {d.value}"}
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

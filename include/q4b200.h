@@ -12,14 +12,16 @@
  *   blocks     uint8 [K/32, N, 18]  interchange format, bit-exact with the reference's
  *              quantize_ggml_q4_0 (quantization.py:307-371): fp16 scale d (little endian),
  *              then 16 bytes, byte j = q[2j] | q[2j+1] << 4.
- *   prepacked  uint8 [ceil(K/64), ceil(N/16), 576]  internal streaming format, one 576-byte
- *              tile per 16 output columns x 64 k.  Same information as `blocks` (18 bytes per
- *              32 weights), rearranged so that a warp reads a tile with one 128-bit load per
- *              lane plus one 64-bit load of scales.  q4b_prepacked_bytes gives its size; the
- *              buffer must be 16-byte aligned.  Tile layout:
- *                bytes [0,512): 32 slots of 16 bytes; slot p = c*8 + g (g = p%8 column-in-
- *                  octet, c = p/8 k-octet) holds four 32-bit words: blocks (kb0,g),(kb0,g+8),
- *                  (kb0+1,g),(kb0+1,g+8), each word = the 8 nibbles q[8c..8c+7] of that block
+ *   prepacked  uint8 [ceil(N/16), ceil(K/64), 576]  internal streaming format, one 576-byte
+ *              tile per 16 output columns x 64 k, column-tile-major (all k tiles of a column
+ *              tile are contiguous).  Same information as `blocks` (18 bytes per 32 weights),
+ *              rearranged so that a lane's mma fragment is one 128-bit word plus one 64-bit
+ *              word of scales.  q4b_prepacked_bytes gives its size; the buffer must be
+ *              16-byte aligned.  Tile layout:
+ *                bytes [0,512): 32 slots of 16 bytes; the slot of column-in-octet g (0..7) and
+ *                  k-octet c (0..3) is p = (g/2)*8 + (g%2)*4 + (c ^ (g/2)) and holds four
+ *                  32-bit words: blocks (kb0,g),(kb0,g+8),(kb0+1,g),(kb0+1,g+8), each word =
+ *                  the 8 nibbles q[8c..8c+7] of that block
  *                  stored as q0|q2<<4|q4<<8|q6<<12|q1<<16|q3<<20|q5<<24|q7<<28;
  *                bytes [512,576): 8 rows g of four fp16 scales d(kb0,g), d(kb0,g+8),
  *                  d(kb0+1,g), d(kb0+1,g+8).
@@ -108,11 +110,11 @@ Q4B_API int q4b_dequantize(const void *blocks, int64_t K, int64_t N, void *w_out
  * leading dimension ldx (elements, multiple of 8, X 16-byte aligned); Y has leading
  * dimension ldy (elements).
  *
- *   q4b_gemv   decode path, 1 <= M <= 16: streams the prepacked tiles once with 128-bit
- *              loads, dequantises in registers, warp-level mma + split-K reduction in the CTA.
+ *   q4b_gemv   decode path, 1 <= M <= 16: streams the prepacked tiles once (bulk asynchronous
+ *              copies into per-warp rings, 128-bit reads), dequantises in registers,
+ *              warp-level mma + split-K reduction in the CTA.
  *   q4b_gemm   prefill path, any M >= 1 (intended for M >= 17): TMA -> shared memory ->
  *              dequantise to bf16/fp16 -> tcgen05.mma with TMEM accumulators.
- *              Needs K % 64 == 0, ldx % 8 == 0, ldy % 8 == 0 and 16-byte aligned X and Y.
  *   q4b_matmul picks q4b_gemv for M <= 16, otherwise q4b_gemm.
  */
 Q4B_API int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
@@ -123,12 +125,13 @@ Q4B_API int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const
                int64_t K, int64_t N, void *y, int64_t ldy, int flags, void *stream);
 
 /*
- * The tcgen05 kernel bounds every mbarrier wait; a wait that gives up makes the kernel set a
- * word in a small per-device status buffer and return early.  This call synchronises the
- * stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with *detail (may be
- * NULL) = which wait gave up.  It never traps or faults the device.
+ * The matmul kernels bound every mbarrier wait; a wait that gives up makes the kernel set a
+ * status word on the device and stop early (its output is then incomplete).  This call
+ * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with
+ * *detail (may be NULL) = which wait gave up (1..6 prefill kernel roles, 100 decode kernel).
+ * It never traps or faults the device.
  */
-Q4B_API int q4b_gemm_status(void *stream, int *detail);
+Q4B_API int q4b_wait_status(void *stream, int *detail);
 
 /*
  * Host-buffer convenience used for end-to-end timing: x_host and y_host are (ideally pinned)

@@ -3,7 +3,7 @@
 Exports the hot-path names of the reference package (``packages/metalcore/src/metalcore/
 __init__.py:38-39,174-184``) with the same signatures.  All compute runs in hand-written CUDA
 kernels behind the C ABI of ``include/q4b200.h``; importing this package loads that library and
-raises if it has not been built (``python -m metalops_b200.build``).
+raises if it has not been built (``python metalops_b200/build.py``).
 """
 from . import _cabi
 

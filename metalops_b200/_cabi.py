@@ -36,7 +36,7 @@ SYMBOLS = {
     "q4b_gemv": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_gemm": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
-    "q4b_gemm_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
+    "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
     "q4b_matmul_host": (_ci, [_vp, _vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp, _ci, _vp]),
 }
 
@@ -49,7 +49,7 @@ def load() -> ctypes.CDLL:
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             raise ImportError(
-                f"{LIB_PATH} is missing: build it with `python -m metalops_b200.build` "
+                f"{LIB_PATH} is missing: build it with `python metalops_b200/build.py` "
                 "(needs nvcc). This package has no CPU or PyTorch fallback.")
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SYMBOLS.items():

@@ -1,6 +1,6 @@
 """Build step: compiles the CUDA sources under ``csrc/`` into ``libq4b200.so`` next to this file.
 
-    python -m metalops_b200.build [--force] [--verbose]
+    python metalops_b200/build.py [--force] [--verbose]
 
 nvcc cross-compiles for sm_100a without a GPU.  The library links the static CUDA runtime and
 has no link-time dependency on the driver library, so it also loads on a machine without a

@@ -23,6 +23,21 @@ __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + 
 __host__ __device__ inline int64_t tiles_k(int64_t K) { return ceil_div(K, TILE_K); }
 __host__ __device__ inline int64_t tiles_n(int64_t N) { return ceil_div(N, TILE_N); }
 
+// Tiles are stored column-tile-major: all k tiles of 16 output columns are contiguous, so the
+// decode kernel streams one long run per column tile.
+__host__ __device__ inline size_t tile_offset(int64_t nt, int64_t ku, int64_t KU) {
+    return (size_t)(nt * KU + ku) * TILE_BYTES;
+}
+// Position (16-byte slot index) inside a tile of the words belonging to column-in-octet g
+// (0..7) and k-octet c (0..3).  The XOR makes both access patterns bank-conflict free when the
+// tile sits in shared memory: the decode kernel's lane 4g+c, and the prefill kernel's lane
+// 8c+g, each touch eight distinct 16-byte bank groups per quarter warp.
+__host__ __device__ inline int slot_of(int g, int c) { return (g >> 1) * 8 + (g & 1) * 4 + (c ^ (g >> 1)); }
+__host__ __device__ inline void slot_inverse(int p, int &g, int &c) {
+    g = (p >> 3) * 2 + ((p >> 2) & 1);
+    c = (p & 3) ^ (p >> 3);
+}
+
 // ---- nibble order ---------------------------------------------------------------------
 // Interchange word (4 consecutive nibble bytes of a block): byte j = q[2j] | q[2j+1] << 4.
 // Prepacked word: q0 | q2<<4 | q4<<8 | q6<<12 | q1<<16 | q3<<20 | q5<<24 | q7<<28, so that

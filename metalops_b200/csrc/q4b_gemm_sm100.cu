@@ -5,8 +5,8 @@
 // core_mps.mm:5917-5975) for M above the decode range.
 //
 // One persistent CTA per SM, tile 128 (M) x 256 (N) x 64 (K) per pipeline stage:
-//   warp 0      producer: TMA tile load of X (128 x 64, 128-byte swizzle) and one bulk copy of
-//               the stage's packed weights (16 prepacked tiles = 9216 contiguous bytes)
+//   warp 0      producer: TMA tile load of X (128 x 64, 128-byte swizzle) and bulk copies of
+//               the stage's packed weights (16 prepacked tiles of 576 bytes)
 //   warps 6-13  dequantise the packed stage into the K-major, 128-byte-swizzled bf16/fp16 B
 //               operand in shared memory ((q-8)*d, one rounding), then fence to the async proxy
 //   warp 1      one thread issues tcgen05.mma (kind::f16, M128 N256 K16) x 4 per stage,
@@ -207,8 +207,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                     if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag, 1)) goto done;
                     mbar_arrive_expect_tx(bar_full(stage), (uint32_t)(A_BYTES + valid * TILE_BYTES));
                     tma_load_2d(base + SMEM_A + stage * A_BYTES, &tmap_x, ks * BK, mt * BM, bar_full(stage));
-                    bulk_load(base + SMEM_W + stage * W_BYTES, prepacked + ((size_t)ks * NT + nt0) * TILE_BYTES,
-                              (uint32_t)(valid * TILE_BYTES), bar_full(stage));
+                    // the stage's column tiles are k_stages tiles apart in the column-tile-major layout
+                    for (int i = 0; i < valid; ++i)
+                        bulk_load(base + SMEM_W + stage * W_BYTES + i * TILE_BYTES,
+                                  prepacked + tile_offset(nt0 + i, ks, k_stages), TILE_BYTES, bar_full(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -299,7 +301,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                 for (int i = 0; i < W_TILES / NUM_DEQ_WARPS; ++i) {
                     const int tl = dw * (W_TILES / NUM_DEQ_WARPS) + i;
                     if (tl < valid) {
-                        const uint4 qw = *reinterpret_cast<const uint4 *>(wst + tl * TILE_BYTES + (c * 8 + g) * 16);
+                        const uint4 qw = *reinterpret_cast<const uint4 *>(wst + tl * TILE_BYTES + slot_of(g, c) * 16);
                         const uint2 dq = *reinterpret_cast<const uint2 *>(wst + tl * TILE_BYTES + TILE_QS_BYTES + g * 8);
                         const uint32_t words[4] = {qw.x, qw.y, qw.z, qw.w};
                         const uint16_t dbits[4] = {(uint16_t)(dq.x & 0xFFFF), (uint16_t)(dq.x >> 16),
@@ -382,6 +384,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
 }  // namespace gemm
 
 int device_sm_count();
+int gemv_wait_status(int *value);
 
 }  // namespace q4b
 
@@ -416,15 +419,16 @@ extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
                : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st);
 }
 
-extern "C" int q4b_gemm_status(void *stream, int *detail) {
+extern "C" int q4b_wait_status(void *stream, int *detail) {
     Q4B_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
-    int h = 0;
+    int h = 0, hv = 0;
     Q4B_CUDA_TRY(cudaMemcpyFromSymbol(&h, gemm::g_gemm_status, sizeof(int)));
-    if (detail) *detail = h;
     if (h != 0) {
         const int zero = 0;
         Q4B_CUDA_TRY(cudaMemcpyToSymbol(gemm::g_gemm_status, &zero, sizeof(int)));
-        return Q4B_ERR_TIMEOUT;
     }
-    return Q4B_OK;
+    if (int rc = gemv_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (detail) *detail = h;
+    return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;
 }

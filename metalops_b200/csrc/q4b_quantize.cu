@@ -149,7 +149,7 @@ quantize_kn_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
                 sb[1 + 2 * c] = (uint16_t)(iw & 0xFFFF);
                 sb[2 + 2 * c] = (uint16_t)(iw >> 16);
             }
-            *reinterpret_cast<uint32_t *>(tile + (c * 8 + g) * 16 + (kbl * 2 + hi8) * 4) =
+            *reinterpret_cast<uint32_t *>(tile + slot_of(g, c) * 16 + (kbl * 2 + hi8) * 4) =
                 interchange_to_prepacked_word(iw);
         }
         *reinterpret_cast<uint16_t *>(tile + TILE_QS_BYTES + g * 8 + (kbl * 2 + hi8) * 2) = dbits;
@@ -159,9 +159,12 @@ quantize_kn_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
     const int64_t nt0 = n0 / TILE_N;
     if (prepacked != nullptr) {
         const int ntiles = (int)min((int64_t)(QT_N / TILE_N), NT - nt0);
-        uint4 *dst = reinterpret_cast<uint4 *>(prepacked + (size_t)(ku * NT + nt0) * TILE_BYTES);
+        const int64_t KU = tiles_k(K);
         const uint4 *src = reinterpret_cast<const uint4 *>(&s_tile[0][0]);
-        for (int i = tid; i < ntiles * (TILE_BYTES / 16); i += QT_THREADS) dst[i] = src[i];
+        for (int i = tid; i < ntiles * (TILE_BYTES / 16); i += QT_THREADS) {
+            const int t = i / (TILE_BYTES / 16), o = i % (TILE_BYTES / 16);
+            reinterpret_cast<uint4 *>(prepacked + tile_offset(nt0 + t, ku, KU))[o] = src[i];
+        }
     }
     if (blocks != nullptr) {
         const int ncols = (int)min((int64_t)QT_N, N - n0);
@@ -249,7 +252,7 @@ quantize_nk_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
     }
     const int g = r & 7, hi8 = r >> 3;
     uint8_t *tile = s_tile[kbl >> 1];
-    *reinterpret_cast<uint32_t *>(tile + (c * 8 + g) * 16 + ((kbl & 1) * 2 + hi8) * 4) =
+    *reinterpret_cast<uint32_t *>(tile + slot_of(g, c) * 16 + ((kbl & 1) * 2 + hi8) * 4) =
         interchange_to_prepacked_word(iw);
     if (c == 0) *reinterpret_cast<uint16_t *>(tile + TILE_QS_BYTES + g * 8 + ((kbl & 1) * 2 + hi8) * 2) = dbits;
     const int64_t n0 = nt * TILE_N;
@@ -262,13 +265,13 @@ quantize_nk_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
     }
     __syncthreads();
     if (prepacked != nullptr) {
-        // the CTA's four tiles are NT tiles apart in the [ku][nt] order: copy each on its own
+        // the CTA's four tiles are consecutive k tiles of one column tile: contiguous in memory
         const int64_t ku0 = kb0 / TILE_KB;
         const int64_t KU = tiles_k(K);
         for (int i = tid; i < (QNK_KB / TILE_KB) * (TILE_BYTES / 16); i += QNK_THREADS) {
             const int t = i / (TILE_BYTES / 16), o = i % (TILE_BYTES / 16);
             if (ku0 + t < KU)
-                reinterpret_cast<uint4 *>(prepacked + (size_t)((ku0 + t) * NT + nt) * TILE_BYTES)[o] =
+                reinterpret_cast<uint4 *>(prepacked + tile_offset(nt, ku0 + t, KU))[o] =
                     reinterpret_cast<const uint4 *>(&s_tile[t][0])[o];
         }
     }
@@ -290,8 +293,10 @@ repack_kernel(const uint8_t *__restrict__ blocks, int64_t K, int64_t N, uint8_t 
     const int64_t KB = K / QK, NT = tiles_n(N), KU = tiles_k(K);
     const int64_t tile_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (tile_id >= NT * KU) return;
-    const int64_t ku = tile_id / NT, nt = tile_id % NT;
-    const int p = threadIdx.x & 31, c = p >> 3, g = p & 7;
+    const int64_t nt = tile_id / KU, ku = tile_id % KU;
+    const int p = threadIdx.x & 31;
+    int g, c;
+    slot_inverse(p, g, c);
     uint32_t wds[4];
     uint16_t ds[4];
 #pragma unroll
@@ -309,7 +314,7 @@ repack_kernel(const uint8_t *__restrict__ blocks, int64_t K, int64_t N, uint8_t 
     }
     uint8_t *tile = prepacked + (size_t)tile_id * TILE_BYTES;
     *reinterpret_cast<uint4 *>(tile + p * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-    if (c == 0)
+    if (c == 0)      // the scales of row g are the same for every k-octet; one lane writes them
         *reinterpret_cast<uint2 *>(tile + TILE_QS_BYTES + g * 8) =
             make_uint2((uint32_t)ds[0] | ((uint32_t)ds[1] << 16), (uint32_t)ds[2] | ((uint32_t)ds[3] << 16));
 }
@@ -320,8 +325,10 @@ unpack_kernel(const uint8_t *__restrict__ prepacked, int64_t K, int64_t N, uint8
     const int64_t KB = K / QK, NT = tiles_n(N), KU = tiles_k(K);
     const int64_t tile_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (tile_id >= NT * KU) return;
-    const int64_t ku = tile_id / NT, nt = tile_id % NT;
-    const int p = threadIdx.x & 31, c = p >> 3, g = p & 7;
+    const int64_t nt = tile_id / KU, ku = tile_id % KU;
+    const int p = threadIdx.x & 31;
+    int g, c;
+    slot_inverse(p, g, c);
     const uint8_t *tile = prepacked + (size_t)tile_id * TILE_BYTES;
     const uint4 qw = __ldg(reinterpret_cast<const uint4 *>(tile + p * 16));
     const uint2 dw = __ldg(reinterpret_cast<const uint2 *>(tile + TILE_QS_BYTES + g * 8));

@@ -176,17 +176,17 @@ def _matmul_prepacked(X: torch.Tensor, pre: Q4Prepacked, out: Optional[torch.Ten
     return y.float() if in_dtype == torch.float32 else y
 
 
-def gemm_status(device=None) -> int:
+def wait_status(device=None) -> int:
     """Synchronise the current stream and return the prefill kernel's bounded-wait status:
     0 when every wait completed, else the code of the first wait that gave up (also raises)."""
     import ctypes
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     detail = ctypes.c_int(0)
     with torch.cuda.device(dev):
-        rc = _cabi.load().q4b_gemm_status(_cabi.stream_ptr(dev), ctypes.byref(detail))
+        rc = _cabi.load().q4b_wait_status(_cabi.stream_ptr(dev), ctypes.byref(detail))
     if rc == _cabi.ERR_TIMEOUT:
         raise RuntimeError(f"q4b_gemm: a bounded device-side wait gave up (code {detail.value})")
-    _cabi.check(rc, "q4b_gemm_status")
+    _cabi.check(rc, "q4b_wait_status")
     return detail.value
 
 

@@ -15,8 +15,9 @@ def header_symbols():
 
 
 def test_library_exports_every_declared_symbol():
-    from metalops_b200 import _cabi, build
-    build.build()
+    import __graft_entry__
+    __graft_entry__.build()
+    from metalops_b200 import _cabi
     lib = ctypes.CDLL(_cabi.LIB_PATH)
     declared = header_symbols()
     assert len(declared) >= 14

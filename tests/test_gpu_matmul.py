@@ -163,7 +163,7 @@ def test_int4_linear_module(mo, cuda_dev):
 def check_gemm(mo, dev, w, x, tol):
     from metalops_b200 import quantization as Q
     err = check(mo, dev, w, x, tol, kernel="gemm")
-    assert Q.gemm_status(dev) == 0
+    assert Q.wait_status(dev) == 0
     return err
 
 
@@ -204,7 +204,7 @@ def test_config3_prefill_with_outliers(mo, cuda_dev, M):
     blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
     xd = x.to(cuda_dev)
     y = mo.matmul_ggml_q4_0(xd, blocks)
-    assert Q.gemm_status(cuda_dev) == 0
+    assert Q.wait_status(cuda_dev) == 0
     g = torch.Generator().manual_seed(9)
     rows = torch.randperm(M, generator=g)[:256].sort().values
     cols = torch.randperm(14336, generator=g)[:1024].sort().values
@@ -224,7 +224,7 @@ def test_config5_gemm_sweep(mo, cuda_dev, M):
     w, x = make_case(1005 + M, M, 4096, 14336, torch.float16)
     blocks = mo.quantize_ggml_q4_0(w.half().to(cuda_dev))
     y = mo.matmul_ggml_q4_0(x.to(cuda_dev), blocks)
-    assert Q.gemm_status(cuda_dev) == 0
+    assert Q.wait_status(cuda_dev) == 0
     g = torch.Generator().manual_seed(M)
     rows = torch.randperm(M, generator=g)[:32].sort().values
     cols = torch.randperm(14336, generator=g)[:2048].sort().values
