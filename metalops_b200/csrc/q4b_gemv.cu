@@ -5,17 +5,19 @@
 // core_mps.mm:5917-5975), which has no GEMV specialisation.
 //
 // Each warp owns one 16-column tile and a contiguous range of its k tiles, which is one
-// contiguous run of bytes in the column-tile-major prepacked layout.  Lane 0 feeds a per-warp
-// ring in shared memory with bulk asynchronous copies (cp.async.bulk, completion counted on an
-// mbarrier per ring slot), so the bytes in flight per SM are set by the ring size, not by
-// registers.  Lanes read their 16 bytes of nibbles and 8 bytes of scales from the ring
-// (conflict free), turn the nibbles into (q-8) fp16/bf16 pairs in registers, and feed them as
-// the 16-row A operand of mma.sync.m16n8k16; up to 8 activation rows are the B operand, so
-// M = 1..8 costs the same and M = 9..16 one more fragment.  The per-block scale multiplies the
-// fp32 partial product of each 32-k block; accumulation is fp32 throughout.  Warps of a CTA
-// that share a column tile split k and are reduced through shared memory.
+// contiguous run of bytes in the column-tile-major prepacked layout.  The warp keeps a private
+// ring in shared memory fed by bulk asynchronous copies (cp.async.bulk, completion counted on
+// one mbarrier per ring slot): a slot holds CHUNK weight tiles plus the matching k-slice of the
+// activation rows, so both arrive ahead of use and the bytes in flight per SM are set by the
+// ring size, not by registers.  Lanes read 16 bytes of nibbles, 8 bytes of scales and 16 bytes
+// of x per 32-k block from the slot (all conflict free), turn the nibbles into (q-8)
+// fp16/bf16 pairs in registers, and feed them as the 16-row A operand of mma.sync.m16n8k16;
+// up to 8 activation rows are the B operand, so M = 1..8 costs the same and M = 9..16 one more
+// fragment.  The per-block scale multiplies the fp32 partial product of each 32-k block;
+// accumulation is fp32 throughout.  Warps of a CTA that share a column tile split k and are
+// reduced through shared memory.
 //
-// Every mbarrier wait is bounded: a wait that gives up sets g_wait_status, and the warp stops
+// Every mbarrier wait is bounded: a wait that gives up sets g_wait_status and the warp stops
 // consuming (its outputs are then wrong, which the status reports) instead of spinning.
 #include "q4b_common.cuh"
 
@@ -23,16 +25,28 @@ namespace q4b {
 
 constexpr int GEMV_WARPS = 8;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
-constexpr int GEMV_CHUNK = 4;                       // tiles per bulk copy (2304 bytes)
-constexpr int GEMV_SLOTS = 3;                       // ring slots per warp
-constexpr int GEMV_SLOT_BYTES = GEMV_CHUNK * TILE_BYTES;
-constexpr int GEMV_RING_BYTES = GEMV_SLOTS * GEMV_SLOT_BYTES;          // 6912 per warp
-constexpr int GEMV_SMEM_DYN = GEMV_WARPS * GEMV_RING_BYTES;            // 55296 per CTA: 3 CTAs per SM
 constexpr int GEMV_SPIN_LIMIT = 1 << 22;            // try_wait polls before giving up (~0.1 s)
 
 __device__ int g_wait_status = 0;                  // first bounded wait of this file that gave up
 
+// Shared-memory geometry of one ring slot: CHUNK weight tiles, then the x rows.  The row
+// stride is 64 bytes more than a multiple of 128 so that the eight (row, k-octet) pairs a
+// quarter warp reads fall into eight different 16-byte bank groups.
+template <int CHUNK> struct SlotGeom {
+    static constexpr int W_BYTES = CHUNK * TILE_BYTES;
+    static constexpr int X_ROW = CHUNK * TILE_K * 2;          // bytes of one activation row slice
+    static constexpr int X_STRIDE = X_ROW + 64;
+    static __host__ __device__ constexpr int slot_bytes(int m) { return W_BYTES + m * X_STRIDE; }
+};
+
 __device__ __forceinline__ uint32_t smem_addr_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
 template <bool BF16>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -54,13 +68,15 @@ template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
 }
 
 // KS = warps of a CTA that split k for the same column tile; the CTA covers 8/KS column tiles.
-template <bool BF16, int MF, int KS>
+// CHUNK tiles per ring slot, SLOTS slots per warp.
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *__restrict__ prepacked, int64_t K,
             int64_t N, uint16_t *__restrict__ y, int64_t ldy) {
+    using G = SlotGeom<CHUNK>;
     constexpr int NTC = GEMV_WARPS / KS;
     extern __shared__ __align__(128) uint8_t ring_all[];
-    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][GEMV_SLOTS];
+    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][SLOTS];
     __shared__ float red[GEMV_WARPS][MF][TILE_N * 8];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -72,37 +88,59 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     const bool active = nt < NT;
     const int ku0 = (int)((int64_t)KU * ks / KS), ku1 = (int)((int64_t)KU * (ks + 1) / KS);
     const int ntiles = active ? ku1 - ku0 : 0;
-    const int nchunks = (ntiles + GEMV_CHUNK - 1) / GEMV_CHUNK;
+    const int nchunks = (ntiles + CHUNK - 1) / CHUNK;
+    const int slot_bytes = G::slot_bytes(M);
 
-    const uint8_t *ring = ring_all + warp * GEMV_RING_BYTES;
+    uint8_t *ring = ring_all + (size_t)warp * SLOTS * slot_bytes;
     const uint32_t ring_s = smem_addr_u32(ring);
     const uint32_t bar_s = smem_addr_u32(&bars[warp][0]);
-    const uint8_t *src = prepacked + tile_offset(active ? nt : 0, ku0, KU);
+    const uint8_t *wsrc = prepacked + tile_offset(active ? nt : 0, ku0, KU);
+    const int64_t kbase = (int64_t)ku0 * TILE_K;
 
-    auto issue = [&](int ci) {          // lane 0 only: arm the slot and start its bulk copy
-        const int slot = ci % GEMV_SLOTS;
-        const uint32_t bytes = (uint32_t)(min(GEMV_CHUNK, ntiles - ci * GEMV_CHUNK) * TILE_BYTES);
+    // lane 0: arm the slot for the weight bytes and start their copy
+    auto issue_w = [&](int ci, int slot) {
+        const uint32_t bytes = (uint32_t)(min(CHUNK, ntiles - ci * CHUNK) * TILE_BYTES);
         const uint32_t bar = bar_s + 8u * slot;
-        asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(ring_s + (uint32_t)(slot * GEMV_SLOT_BYTES)), "l"(src + (size_t)ci * GEMV_SLOT_BYTES), "r"(bytes), "r"(bar)
-                     : "memory");
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(ring_s + (uint32_t)(slot * slot_bytes), wsrc + (size_t)ci * G::W_BYTES, bytes, bar);
+    };
+    // lanes 0..M-1: one activation row slice each (lane 0 arms the barrier for all of them)
+    auto issue_x = [&](int ci, int slot) {
+        const int64_t k0 = kbase + (int64_t)ci * CHUNK * TILE_K;
+        const uint32_t row_bytes = (uint32_t)(min((int64_t)CHUNK * TILE_K, K - k0) * 2);
+        const uint32_t bar = bar_s + 8u * slot;
+        if (lane == 0) mbar_expect_tx(bar, row_bytes * (uint32_t)M);
+        __syncwarp();
+        if (lane < M)
+            bulk_g2s(ring_s + (uint32_t)(slot * slot_bytes + G::W_BYTES + lane * G::X_STRIDE),
+                     x + (size_t)lane * ldx + k0, row_bytes, bar);
     };
 
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < GEMV_SLOTS; ++s)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s + 8u * s) : "memory");
+        for (int s = 0; s < SLOTS; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(bar_s + 8u * s) : "memory");   // weights + x
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 #pragma unroll
-        for (int s = 0; s < GEMV_SLOTS; ++s)
-            if (s < nchunks) issue(s);
+        for (int s = 0; s < SLOTS; ++s)
+            if (s < nchunks) issue_w(s, s);
+    }
+    if (K % TILE_K) {
+        // Odd number of 32-k blocks: the last tile's pad block has zero weights, but what it is
+        // multiplied with must be finite, so the x slices start out as zeros.
+        for (int s = 0; s < SLOTS; ++s)
+            for (int i = lane * 16; i < M * G::X_STRIDE; i += 32 * 16)
+                *reinterpret_cast<uint4 *>(ring + s * slot_bytes + G::W_BYTES + i) = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
     // Weights never depend on earlier kernels of the stream; x and y do.  Under programmatic
-    // dependent launch the copies above overlap the previous kernel's tail.
+    // dependent launch the weight copies above overlap the previous kernel's tail.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s)
+        if (s < nchunks) issue_x(s, s);
 
     float acc[MF][4];
 #pragma unroll
@@ -111,17 +149,16 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
         for (int i = 0; i < 4; ++i) acc[f][i] = 0.0f;
     const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-    const uint4 *xrow[MF];
-#pragma unroll
-    for (int f = 0; f < MF; ++f)
-        xrow[f] = reinterpret_cast<const uint4 *>(x + (size_t)min(f * 8 + g, M - 1) * ldx + c * 8);
-
     const int qoff = slot_of(g, c) * 16, doff = TILE_QS_BYTES + g * 8;
-    bool ok = true;
-    for (int ci = 0; ci < nchunks && ok; ++ci) {
-        const int slot = ci % GEMV_SLOTS;
-        const uint32_t parity = (uint32_t)((ci / GEMV_SLOTS) & 1);
+    int xoff[MF];
+#pragma unroll
+    for (int f = 0; f < MF; ++f) xoff[f] = G::W_BYTES + min(f * 8 + g, M - 1) * G::X_STRIDE + c * 16;
+
+    int slot = 0;
+    uint32_t parity = 0;
+    for (int ci = 0; ci < nchunks; ++ci) {
         const uint32_t bar = bar_s + 8u * slot;
+        bool ok = true;
         int spins = 0;
         while (true) {
             uint32_t done;
@@ -134,19 +171,16 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
                 break;
             }
         }
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const uint8_t *sl = ring + slot * GEMV_SLOT_BYTES;
-        const int tiles_here = min(GEMV_CHUNK, ntiles - ci * GEMV_CHUNK);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        const uint8_t *sl = ring + slot * slot_bytes;
+        const int tiles_here = min(CHUNK, ntiles - ci * CHUNK);
 #pragma unroll
-        for (int t = 0; t < GEMV_CHUNK; ++t) {
+        for (int t = 0; t < CHUNK; ++t) {
             if (t < tiles_here) {
                 const uint4 qw = *reinterpret_cast<const uint4 *>(sl + t * TILE_BYTES + qoff);
                 const uint2 dw = *reinterpret_cast<const uint2 *>(sl + t * TILE_BYTES + doff);
-                const int ku = ku0 + ci * GEMV_CHUNK + t;
 #pragma unroll
                 for (int kbl = 0; kbl < TILE_KB; ++kbl) {
-                    const int64_t k = (int64_t)ku * TILE_K + kbl * QK;
                     uint32_t hlo[4], hhi[4];
                     dequant_word<BF16>(kbl ? qw.z : qw.x, hlo);     // column g
                     dequant_word<BF16>(kbl ? qw.w : qw.y, hhi);     // column g + 8
@@ -154,8 +188,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
                     const float2 df = __half22float2(dh);           // (d of column g, d of column g+8)
 #pragma unroll
                     for (int f = 0; f < MF; ++f) {
-                        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-                        if (k < K) xv = xrow[f][k >> 3];            // the pad block of an odd K/32 has d = 0
+                        const uint4 xv = *reinterpret_cast<const uint4 *>(sl + xoff[f] + (t * TILE_K + kbl * QK) * 2);
                         float part[4];
                         mma16816<BF16>(part, hlo[0], hhi[0], hlo[1], hhi[1], xv.x, xv.y, zero4);
                         mma16816<BF16>(part, hlo[2], hhi[2], hlo[3], hhi[3], xv.z, xv.w, part);
@@ -168,7 +201,11 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
             }
         }
         __syncwarp();                    // every lane has consumed the slot before it is refilled
-        if (lane == 0 && ci + GEMV_SLOTS < nchunks) issue(ci + GEMV_SLOTS);
+        if (ci + SLOTS < nchunks) {
+            if (lane == 0) issue_w(ci + SLOTS, slot);
+            issue_x(ci + SLOTS, slot);
+        }
+        if (++slot == SLOTS) { slot = 0; parity ^= 1; }
     }
 
     // acc[f][0..1] = column g, rows f*8 + 2c, 2c+1 ; acc[f][2..3] = column g+8, same rows
@@ -180,11 +217,10 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
         red[warp][f][(2 * c + 1) * TILE_N + g + 8] = acc[f][3];
     }
     __syncthreads();
-    const int mrows = min(M - 0, MF * 8);
-    for (int o = threadIdx.x; o < NTC * mrows * TILE_N; o += GEMV_THREADS) {
+    for (int o = threadIdx.x; o < NTC * M * TILE_N; o += GEMV_THREADS) {
         const int nl = o % TILE_N;
-        const int m = (o / TILE_N) % mrows;
-        const int tl = o / (TILE_N * mrows);
+        const int m = (o / TILE_N) % M;
+        const int tl = o / (TILE_N * M);
         const int f = m >> 3, m8 = m & 7;
         const int64_t n = ((int64_t)blockIdx.x * NTC + tl) * TILE_N + nl;
         if (n < N) {
@@ -196,41 +232,55 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     }
 }
 
-template <bool BF16, int MF, int KS>
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
 static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
                        int64_t ldy, int flags, cudaStream_t st) {
     constexpr int NTC = GEMV_WARPS / KS;
+    const int smem = GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(M);
     // opt in to > 48 KB of dynamic shared memory once per device and instantiation
     static bool attr_done[64] = {};
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM_DYN));
+        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(MF * 8)));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ceil_div(tiles_n(N), NTC));
     cfg.blockDim = dim3(GEMV_THREADS);
-    cfg.dynamicSmemBytes = GEMV_SMEM_DYN;
+    cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
-    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS>, (const uint16_t *)x, M, ldx,
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
                                     (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy));
     return Q4B_OK;
 }
 
-template <bool BF16, int MF>
+// Ring geometry by row count: shared memory per CTA = 8 warps x SLOTS x (CHUNK x 576 + M x row).
+//   M <= 4 : 4 tiles x 3 slots (66..102 KB, 2-3 CTAs per SM)
+//   M <= 8 : 4 tiles x 2 slots (100 KB)          M <= 16 : 2 tiles x 2 slots (98 KB)
+template <bool BF16, int KS>
+static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
+                         int64_t ldy, int flags, cudaStream_t st) {
+    if (M <= 4) return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    if (M <= 8) return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+}
+
+template <bool BF16>
 static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
                           void *y, int64_t ldy, int flags, cudaStream_t st) {
     switch (ksplit) {
-        case 8: return launch_gemv<BF16, MF, 8>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        case 4: return launch_gemv<BF16, MF, 4>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        case 2: return launch_gemv<BF16, MF, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        default: return launch_gemv<BF16, MF, 1>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        case 8: return launch_gemv_m<BF16, 8>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        case 4: return launch_gemv_m<BF16, 4>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        case 2: return launch_gemv_m<BF16, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        default: return launch_gemv_m<BF16, 1>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
     }
 }
 
@@ -270,10 +320,6 @@ extern "C" int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
     }
     while (ks > 1 && KU < ks) ks /= 2;
     cudaStream_t st = (cudaStream_t)stream;
-    const bool bf = x_dtype == Q4B_BF16;
-    if (M <= 8)
-        return bf ? launch_gemv_ks<true, 1>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st)
-                  : launch_gemv_ks<false, 1>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st);
-    return bf ? launch_gemv_ks<true, 2>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st)
-              : launch_gemv_ks<false, 2>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st);
+    return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st)
+                               : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st);
 }
