@@ -48,17 +48,64 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// d = a . b (first k-step of a block: the C operand is literal zero, no register is cleared)
 template <bool BF16>
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1, const float (&z)[4]) {
+__device__ __forceinline__ void mma16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
     if constexpr (BF16) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z[0]), "f"(z[1]), "f"(z[2]), "f"(z[3]));
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{0f00000000,0f00000000,0f00000000,0f00000000};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     } else {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z[0]), "f"(z[1]), "f"(z[2]), "f"(z[3]));
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{0f00000000,0f00000000,0f00000000,0f00000000};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+// d += a . b
+template <bool BF16>
+__device__ __forceinline__ void mma16816_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    if constexpr (BF16) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// One ring slot: CHUNK tiles (all of them when FULL, else the first tiles_here).  Every shared
+// memory address is the slot base plus a compile-time offset plus a per-lane constant.
+template <bool BF16, int MF, int CHUNK, bool FULL>
+__device__ __forceinline__ void consume_slot(const uint8_t *sl, int qoff, int doff, const int (&xoff)[MF],
+                                             int tiles_here, float (&acc)[MF][4]) {
+#pragma unroll
+    for (int t = 0; t < CHUNK; ++t) {
+        if (FULL || t < tiles_here) {
+            const uint4 qw = *reinterpret_cast<const uint4 *>(sl + t * TILE_BYTES + qoff);
+            const uint2 dw = *reinterpret_cast<const uint2 *>(sl + t * TILE_BYTES + doff);
+#pragma unroll
+            for (int kbl = 0; kbl < TILE_KB; ++kbl) {
+                uint32_t hlo[4], hhi[4];
+                dequant_word<BF16>(kbl ? qw.z : qw.x, hlo);     // column g
+                dequant_word<BF16>(kbl ? qw.w : qw.y, hhi);     // column g + 8
+                const uint32_t dpair = kbl ? dw.y : dw.x;       // (d of column g, d of column g+8)
+                const float dlo = __half2float(__ushort_as_half((uint16_t)(dpair & 0xFFFFu)));
+                const float dhi = __half2float(__ushort_as_half((uint16_t)(dpair >> 16)));
+#pragma unroll
+                for (int f = 0; f < MF; ++f) {
+                    const uint4 xv = *reinterpret_cast<const uint4 *>(sl + xoff[f] + (t * TILE_K + kbl * QK) * 2);
+                    float part[4];
+                    mma16816_first<BF16>(part, hlo[0], hhi[0], hlo[1], hhi[1], xv.x, xv.y);
+                    mma16816_acc<BF16>(part, hlo[2], hhi[2], hlo[3], hhi[3], xv.z, xv.w);
+                    acc[f][0] = fmaf(dlo, part[0], acc[f][0]);
+                    acc[f][1] = fmaf(dlo, part[1], acc[f][1]);
+                    acc[f][2] = fmaf(dhi, part[2], acc[f][2]);
+                    acc[f][3] = fmaf(dhi, part[3], acc[f][3]);
+                }
+            }
+        }
     }
 }
 
@@ -82,11 +129,11 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int ks = warp % KS, ntl = warp / KS;
-    const int64_t NT = tiles_n(N);
+    const int NT = (int)tiles_n(N);
     const int KU = (int)tiles_k(K);
-    const int64_t nt = (int64_t)blockIdx.x * NTC + ntl;
+    const int nt = (int)blockIdx.x * NTC + ntl;
     const bool active = nt < NT;
-    const int ku0 = (int)((int64_t)KU * ks / KS), ku1 = (int)((int64_t)KU * (ks + 1) / KS);
+    const int ku0 = KU * ks / KS, ku1 = KU * (ks + 1) / KS;
     const int ntiles = active ? ku1 - ku0 : 0;
     const int nchunks = (ntiles + CHUNK - 1) / CHUNK;
     const int slot_bytes = G::slot_bytes(M);
@@ -147,7 +194,6 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     for (int f = 0; f < MF; ++f)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[f][i] = 0.0f;
-    const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
     const int qoff = slot_of(g, c) * 16, doff = TILE_QS_BYTES + g * 8;
     int xoff[MF];
@@ -158,48 +204,21 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     uint32_t parity = 0;
     for (int ci = 0; ci < nchunks; ++ci) {
         const uint32_t bar = bar_s + 8u * slot;
-        bool ok = true;
-        int spins = 0;
-        while (true) {
-            uint32_t done;
-            asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-            if (done) break;
-            if (++spins > GEMV_SPIN_LIMIT) {
-                atomicCAS(&g_wait_status, 0, 100);
-                ok = false;
-                break;
-            }
+        uint32_t done;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (!done) {                     // slow path: bounded polling
+            int spins = 0;
+            while (!done && ++spins <= GEMV_SPIN_LIMIT)
+                asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+            if (!done) atomicCAS(&g_wait_status, 0, 100);
         }
-        if (!__all_sync(0xffffffffu, ok)) break;
+        if (!__all_sync(0xffffffffu, done != 0)) break;
         const uint8_t *sl = ring + slot * slot_bytes;
-        const int tiles_here = min(CHUNK, ntiles - ci * CHUNK);
-#pragma unroll
-        for (int t = 0; t < CHUNK; ++t) {
-            if (t < tiles_here) {
-                const uint4 qw = *reinterpret_cast<const uint4 *>(sl + t * TILE_BYTES + qoff);
-                const uint2 dw = *reinterpret_cast<const uint2 *>(sl + t * TILE_BYTES + doff);
-#pragma unroll
-                for (int kbl = 0; kbl < TILE_KB; ++kbl) {
-                    uint32_t hlo[4], hhi[4];
-                    dequant_word<BF16>(kbl ? qw.z : qw.x, hlo);     // column g
-                    dequant_word<BF16>(kbl ? qw.w : qw.y, hhi);     // column g + 8
-                    const __half2 dh = *reinterpret_cast<const __half2 *>(kbl ? &dw.y : &dw.x);
-                    const float2 df = __half22float2(dh);           // (d of column g, d of column g+8)
-#pragma unroll
-                    for (int f = 0; f < MF; ++f) {
-                        const uint4 xv = *reinterpret_cast<const uint4 *>(sl + xoff[f] + (t * TILE_K + kbl * QK) * 2);
-                        float part[4];
-                        mma16816<BF16>(part, hlo[0], hhi[0], hlo[1], hhi[1], xv.x, xv.y, zero4);
-                        mma16816<BF16>(part, hlo[2], hhi[2], hlo[3], hhi[3], xv.z, xv.w, part);
-                        acc[f][0] = fmaf(df.x, part[0], acc[f][0]);
-                        acc[f][1] = fmaf(df.x, part[1], acc[f][1]);
-                        acc[f][2] = fmaf(df.y, part[2], acc[f][2]);
-                        acc[f][3] = fmaf(df.y, part[3], acc[f][3]);
-                    }
-                }
-            }
-        }
+        const int tiles_here = ntiles - ci * CHUNK;
+        if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(sl, qoff, doff, xoff, CHUNK, acc);
+        else consume_slot<BF16, MF, CHUNK, false>(sl, qoff, doff, xoff, tiles_here, acc);
         __syncwarp();                    // every lane has consumed the slot before it is refilled
         if (ci + SLOTS < nchunks) {
             if (lane == 0) issue_w(ci + SLOTS, slot);
@@ -217,13 +236,13 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
         red[warp][f][(2 * c + 1) * TILE_N + g + 8] = acc[f][3];
     }
     __syncthreads();
-    for (int o = threadIdx.x; o < NTC * M * TILE_N; o += GEMV_THREADS) {
+    for (int o = threadIdx.x; o < NTC * MF * 8 * TILE_N; o += GEMV_THREADS) {
         const int nl = o % TILE_N;
-        const int m = (o / TILE_N) % M;
-        const int tl = o / (TILE_N * M);
+        const int m = (o / TILE_N) % (MF * 8);
+        const int tl = o / (TILE_N * MF * 8);
         const int f = m >> 3, m8 = m & 7;
-        const int64_t n = ((int64_t)blockIdx.x * NTC + tl) * TILE_N + nl;
-        if (n < N) {
+        const int n = ((int)blockIdx.x * NTC + tl) * TILE_N + nl;
+        if (m < M && n < N) {
             float s = 0.0f;
 #pragma unroll
             for (int j = 0; j < KS; ++j) s += red[tl * KS + j][f][m8 * TILE_N + nl];
