@@ -142,6 +142,36 @@ Q4B_API int q4b_matmul_host(const void *x_host, void *x_dev, int x_dtype, int64_
                     const void *prepacked, int64_t K, int64_t N, void *y_dev, void *y_host,
                     int flags, void *stream);
 
+/*
+ * Host-buffer product for callers that cannot allocate device memory.  (This entry point has no
+ * counterpart in the reference: metalcore always lets its extension allocate.)
+ *
+ * Who needs it: code that runs where cudaMalloc is forbidden or unaffordable — a plugin called
+ * inside somebody else's real-time or inference loop that must not touch the allocator, a host
+ * that has handed all device memory to one arena and gives none back, a process that may not
+ * take the allocator's device-wide lock.  q4b_matmul_host asks such a caller for two device
+ * staging buffers; here they come out of a fixed array that is part of the library image.
+ *
+ * x_host [M, K] and y_host [M, N] are HOST pointers (dense, x_dtype f16 or bf16), `prepacked` is
+ * the usual device pointer.  Enqueues H2D copy of X, q4b_matmul, D2H copy of Y on `stream`.
+ *
+ * Limits and rules:
+ *   - round_up(M*K*2, 256) + round_up(M*N*2, 256) must not exceed Q4B_NOALLOC_MAX_BYTES, else
+ *     the call returns Q4B_ERR_TOO_LARGE and enqueues nothing.  Every GPU on which the library
+ *     is loaded holds those Q4B_NOALLOC_MAX_BYTES of global memory until the process exits.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current) and keeps it; make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's bytes.
+ *     Nothing in it needs clearing (X's part is overwritten whole, Y's part is written whole
+ *     before it is read), but two calls whose work overlaps on the GPU — different streams, or
+ *     different host threads — race on it.  Serialise them on one stream.
+ *   - No cudaMalloc, cudaFree or allocating library routine is called, on any call.
+ */
+#define Q4B_NOALLOC_MAX_BYTES (4u << 20)
+Q4B_API int q4b_matmul_host_noalloc(const void *x_host, int x_dtype, int64_t M,
+                                    const void *prepacked, int64_t K, int64_t N, void *y_host,
+                                    void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -110,3 +110,59 @@ extern "C" int q4b_matmul_host(const void *x_host, void *x_dev, int x_dtype, int
     Q4B_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, (size_t)M * N * 2, cudaMemcpyDeviceToHost, st));
     return Q4B_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// q4b_matmul_host_noalloc: the same host-buffer product, for callers that cannot allocate device
+// memory.  The two device staging buffers that q4b_matmul_host takes from its caller live in
+// this file-scope array instead.  Every GPU that loads the library carries the array until the
+// process exits, so it is kept modest.
+// ---------------------------------------------------------------------------------------------
+namespace q4b {
+
+constexpr size_t NOALLOC_SCRATCH_BYTES = Q4B_NOALLOC_MAX_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` only names the symbol; it is not a device address.  The real
+// address is asked for once per device, with that device current, and kept here.
+static unsigned char *g_noalloc_ptr[64] = {};
+static std::mutex g_noalloc_mu;
+
+static int noalloc_scratch(unsigned char **out) {
+    int dev = 0;
+    Q4B_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return Q4B_ERR_ARG;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        Q4B_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        if (p == nullptr) return Q4B_ERR_CUDA;
+        g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return Q4B_OK;
+}
+
+}  // namespace q4b
+
+extern "C" int q4b_matmul_host_noalloc(const void *x_host, int x_dtype, int64_t M, const void *prepacked, int64_t K,
+                                       int64_t N, void *y_host, void *stream) {
+    if (x_host == nullptr || prepacked == nullptr || y_host == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || K <= 0 || N <= 0) return Q4B_ERR_ARG;
+    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    if (K % QK) return Q4B_ERR_SHAPE;
+    // X staging first, Y staging after it, both on 256-byte boundaries
+    const size_t x_bytes = ((size_t)M * (size_t)K * 2 + 255) & ~(size_t)255;
+    const size_t y_bytes = ((size_t)M * (size_t)N * 2 + 255) & ~(size_t)255;
+    if (x_bytes > NOALLOC_SCRATCH_BYTES || y_bytes > NOALLOC_SCRATCH_BYTES - x_bytes) return Q4B_ERR_TOO_LARGE;
+    unsigned char *scratch = nullptr;
+    if (int rc = noalloc_scratch(&scratch)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    void *x_dev = scratch, *y_dev = scratch + x_bytes;
+    // Nothing in the scratch has to start at zero: the copy overwrites all of X's staging and the
+    // kernel writes every element of Y's before the copy back reads it.
+    Q4B_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, st));
+    int rc = q4b_matmul(x_dev, x_dtype, M, K, prepacked, K, N, y_dev, N, Q4B_FLAG_NONE, stream);
+    if (rc != Q4B_OK) return rc;
+    Q4B_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, (size_t)M * N * 2, cudaMemcpyDeviceToHost, st));
+    return Q4B_OK;
+}
