@@ -4,15 +4,19 @@
 // (packages/metalcore/src/metalcore/native/quant_kernels.metal:1738-1886, launched by
 // core_mps.mm:5917-5975) for M above the decode range.
 //
-// One persistent CTA per SM, tile 128 (M) x 256 (N) x 64 (K) per pipeline stage:
-//   warp 0      producer: TMA tile load of X (128 x 64, 128-byte swizzle) and bulk copies of
-//               the stage's packed weights (16 prepacked tiles of 576 bytes)
-//   warps 6-13  dequantise the packed stage into the K-major, 128-byte-swizzled bf16/fp16 B
-//               operand in shared memory ((q-8)*d, one rounding), then fence to the async proxy
-//   warp 1      one thread issues tcgen05.mma (kind::f16, M128 N256 K16) x 4 per stage,
-//               accumulating in TMEM; tcgen05.commit releases the stage / publishes the tile
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (double-buffered, 2 x 256 TMEM
-//               columns, so it overlaps the next tile's main loop), convert, 16-byte stores
+// One persistent CTA per SM, tile 256 (M) x 256 (N), 64 k per pipeline step.  The two 128-row
+// halves of the tile are two UMMA instructions that share the dequantised B operand, so every
+// weight is dequantised once per 256 rows of X.  Three independent rings in shared memory:
+//   A ring (3 x 32 KB)  warp 0: TMA tile loads of X (256 x 64, 128-byte swizzle)
+//   W ring (4 x 9 KB)   warp 6: bulk copies of the step's packed weights (16 tiles of 576 bytes)
+//   B ring (2 x 32 KB)  warps 7-14 dequantise a W stage into the K-major, 128-byte-swizzled
+//                       bf16/fp16 B operand ((q-8)*d, one rounding) and fence to the async proxy
+//   warp 1      one thread issues tcgen05.mma (kind::f16, M128 N256 K16), 2 halves x 4 per step,
+//               accumulating in TMEM (2 x 256 columns); tcgen05.commit releases A and B stages
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, convert, 16-byte stores; the next
+//               tile's loads and dequantisation run underneath it
+// The W ring is deep because only the dequantisers wait on it; the B ring needs two stages as
+// long as dequantising a stage is faster than its 8 MMAs.
 // Every mbarrier wait is bounded; a wait that gives up records a code in g_gemm_status, raises
 // a CTA-wide abort flag and every role leaves through the common exit that frees TMEM.
 #include <cuda.h>
@@ -24,21 +28,22 @@
 namespace q4b {
 namespace gemm {
 
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 3;
-constexpr int A_BYTES = BM * BK * 2;                 // 16384
+constexpr int BM = 256, BN = 256, BK = 64, HALF_M = 128;
+constexpr int SA = 3, SW = 4, SB = 2;                // ring depths
+constexpr int A_BYTES = BM * BK * 2;                 // 32768
+constexpr int A_HALF_BYTES = HALF_M * BK * 2;        // 16384
 constexpr int B_BYTES = BN * BK * 2;                 // 32768
-constexpr int W_TILES = BN / TILE_N;                 // 16 prepacked tiles per stage
+constexpr int W_TILES = BN / TILE_N;                 // 16 prepacked tiles per step
 constexpr int W_BYTES = W_TILES * TILE_BYTES;        // 9216
 constexpr int NUM_DEQ_WARPS = 8;
-constexpr int FIRST_DEQ_WARP = 6;                   // warps 2..5 are the epilogue
-constexpr int THREADS = (FIRST_DEQ_WARP + NUM_DEQ_WARPS) * 32;   // 448
-constexpr int TMEM_COLS = 512;                       // two 256-column fp32 accumulators
+constexpr int WARP_A = 0, WARP_MMA = 1, WARP_W = 6, FIRST_DEQ_WARP = 7;   // warps 2..5: epilogue
+constexpr int THREADS = (FIRST_DEQ_WARP + NUM_DEQ_WARPS) * 32;   // 480
+constexpr int TMEM_COLS = 512;                       // one 256-column fp32 accumulator per half
 constexpr int SMEM_A = 0;
-constexpr int SMEM_B = SMEM_A + STAGES * A_BYTES;
-constexpr int SMEM_W = SMEM_B + STAGES * B_BYTES;
-constexpr int SMEM_BAR = SMEM_W + STAGES * W_BYTES;
-constexpr int NUM_BARS = 3 * STAGES + 4;
+constexpr int SMEM_B = SMEM_A + SA * A_BYTES;
+constexpr int SMEM_W = SMEM_B + SB * B_BYTES;
+constexpr int SMEM_BAR = SMEM_W + SW * W_BYTES;
+constexpr int NUM_BARS = 2 * (SA + SW + SB) + 2;
 constexpr int SMEM_USED = SMEM_BAR + NUM_BARS * 8 + 16;
 constexpr int SMEM_DYN = SMEM_USED + 1024;           // slack to align the base to 1024 bytes
 constexpr long long WAIT_LIMIT_CYCLES = 1LL << 28;   // ~0.15 s; far above any legitimate wait
@@ -146,6 +151,15 @@ template <bool BF16> __device__ __forceinline__ uint32_t scale_pair(uint16_t dbi
     }
 }
 
+// A ring index with its mbarrier phase
+struct RingPos {
+    int s = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int depth) {
+        if (++s == depth) { s = 0; phase ^= 1; }
+    }
+};
+
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
@@ -158,29 +172,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (base - raw);
     const uint32_t bar0 = base + SMEM_BAR;
-    auto bar_full = [&](int s) { return bar0 + 8u * s; };                    // TMA bytes landed
-    auto bar_fullb = [&](int s) { return bar0 + 8u * (STAGES + s); };        // B operand dequantised
-    auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };    // MMAs of the stage retired
-    auto bar_tfull = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };    // accumulator complete
-    auto bar_tempty = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 + a); };
+    auto bar_full_a = [&](int s) { return bar0 + 8u * s; };                          // X tile landed
+    auto bar_empty_a = [&](int s) { return bar0 + 8u * (SA + s); };                  // its MMAs retired
+    auto bar_full_w = [&](int s) { return bar0 + 8u * (2 * SA + s); };               // packed weights landed
+    auto bar_empty_w = [&](int s) { return bar0 + 8u * (2 * SA + SW + s); };         // dequantisers done reading
+    auto bar_full_b = [&](int s) { return bar0 + 8u * (2 * SA + 2 * SW + s); };      // B operand written
+    auto bar_empty_b = [&](int s) { return bar0 + 8u * (2 * SA + 2 * SW + SB + s); };  // its MMAs retired
+    const uint32_t bar_tfull = bar0 + 8u * (2 * (SA + SW + SB));                     // accumulators complete
+    const uint32_t bar_tempty = bar_tfull + 8u;                                      // accumulators drained
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full(s), 1);
-            mbar_init(bar_fullb(s), NUM_DEQ_WARPS);
-            mbar_init(bar_empty(s), 1);
-        }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(bar_tfull(a), 1);
-            mbar_init(bar_tempty(a), 4);
-        }
+        for (int s = 0; s < SA; ++s) { mbar_init(bar_full_a(s), 1); mbar_init(bar_empty_a(s), 1); }
+        for (int s = 0; s < SW; ++s) { mbar_init(bar_full_w(s), 1); mbar_init(bar_empty_w(s), NUM_DEQ_WARPS); }
+        for (int s = 0; s < SB; ++s) { mbar_init(bar_full_b(s), NUM_DEQ_WARPS); mbar_init(bar_empty_b(s), 1); }
+        mbar_init(bar_tfull, 1);
+        mbar_init(bar_tempty, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == WARP_MMA) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -192,111 +205,126 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     const int NT = (int)tiles_n(N);                    // prepacked 16-column tiles
     const int num_mt = (M + BM - 1) / BM, num_nt = (N + BN - 1) / BN;
     const int num_tiles = num_mt * num_nt;
-    const int k_stages = (K + BK - 1) / BK;
+    const int k_steps = (K + BK - 1) / BK;
 
-    if (warp == 0) {
-        // ---------------- producer ----------------
+    if (warp == WARP_A) {
+        // ---------------- X producer ----------------
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            RingPos a;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-                const int mt = t % num_mt, nt = t / num_mt;
-                const int nt0 = nt * W_TILES;
-                const int valid = min(W_TILES, NT - nt0);
-                for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag, 1)) goto done;
-                    mbar_arrive_expect_tx(bar_full(stage), (uint32_t)(A_BYTES + valid * TILE_BYTES));
-                    tma_load_2d(base + SMEM_A + stage * A_BYTES, &tmap_x, ks * BK, mt * BM, bar_full(stage));
-                    // the stage's column tiles are k_stages tiles apart in the column-tile-major layout
-                    for (int i = 0; i < valid; ++i)
-                        bulk_load(base + SMEM_W + stage * W_BYTES + i * TILE_BYTES,
-                                  prepacked + tile_offset(nt0 + i, ks, k_stages), TILE_BYTES, bar_full(stage));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                const int mt = t % num_mt;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!mbar_wait(bar_empty_a(a.s), a.phase ^ 1, abort_flag, 1)) goto done;
+                    mbar_arrive_expect_tx(bar_full_a(a.s), (uint32_t)A_BYTES);
+                    tma_load_2d(base + SMEM_A + a.s * A_BYTES, &tmap_x, ks * BK, mt * BM, bar_full_a(a.s));
+                    a.advance(SA);
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == WARP_W) {
+        // ---------------- packed-weight producer ----------------
+        if (lane == 0) {
+            RingPos w;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                const int nt0 = (t / num_mt) * W_TILES;
+                const int valid = min(W_TILES, NT - nt0);
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!mbar_wait(bar_empty_w(w.s), w.phase ^ 1, abort_flag, 7)) goto done;
+                    mbar_arrive_expect_tx(bar_full_w(w.s), (uint32_t)(valid * TILE_BYTES));
+                    // the step's column tiles are k_steps tiles apart in the column-tile-major layout
+                    for (int i = 0; i < valid; ++i)
+                        bulk_load(base + SMEM_W + w.s * W_BYTES + i * TILE_BYTES,
+                                  prepacked + tile_offset(nt0 + i, ks, k_steps), TILE_BYTES, bar_full_w(w.s));
+                    w.advance(SW);
+                }
+            }
+        }
+    } else if (warp == WARP_MMA) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BF16, BM, BN);
-            int stage = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 0;
+            constexpr uint32_t idesc = make_idesc(BF16, HALF_M, BN);
+            RingPos a, b;
+            uint32_t tphase = 0;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-                if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1, abort_flag, 2)) goto done;
+                const int mt = t % num_mt;
+                const int halves = (M - mt * BM > HALF_M) ? 2 : 1;     // skip an all-padding lower half
+                if (!mbar_wait(bar_tempty, tphase ^ 1, abort_flag, 2)) goto done;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int ks = 0; ks < k_stages; ++ks) {
-                    if (!mbar_wait(bar_full(stage), phase, abort_flag, 3)) goto done;
-                    if (!mbar_wait(bar_fullb(stage), phase, abort_flag, 4)) goto done;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!mbar_wait(bar_full_a(a.s), a.phase, abort_flag, 3)) goto done;
+                    if (!mbar_wait(bar_full_b(b.s), b.phase, abort_flag, 4)) goto done;
                     tc_fence_after();
-                    const uint64_t adesc = make_kmajor_sw128_desc(base + SMEM_A + stage * A_BYTES);
-                    const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + stage * B_BYTES);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + b.s * B_BYTES);
+                    for (int h = 0; h < halves; ++h) {
+                        const uint64_t adesc = make_kmajor_sw128_desc(base + SMEM_A + a.s * A_BYTES + h * A_HALF_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);   // +32 bytes per k16
-                    tc_commit(bar_empty(stage));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        for (int k = 0; k < BK / 16; ++k)                 // +32 bytes per k16 inside the swizzle atom
+                            tc_mma_f16(tmem_base + (uint32_t)(h * BN), adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                    }
+                    tc_commit(bar_empty_a(a.s));
+                    tc_commit(bar_empty_b(b.s));
+                    a.advance(SA);
+                    b.advance(SB);
                 }
-                tc_commit(bar_tfull(acc));
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1;
+                tc_commit(bar_tfull);
+                tphase ^= 1;
             }
         }
-    } else if (warp < FIRST_DEQ_WARP) {
+    } else if (warp < WARP_W) {
         // ---------------- epilogue ----------------
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
-        int acc = 0;
-        uint32_t acc_phase = 0;
+        uint32_t tphase = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             const int mt = t % num_mt, nt = t / num_mt;
-            if (!mbar_wait(bar_tfull(acc), acc_phase, abort_flag, 5)) goto done;
+            const int halves = (M - mt * BM > HALF_M) ? 2 : 1;
+            if (!mbar_wait(bar_tfull, tphase, abort_flag, 5)) goto done;
             tc_fence_after();
-            const int m = mt * BM + quad * 32 + lane;
             const int n_base = nt * BN;
-            uint16_t *yrow = y + (size_t)m * ldy;
+            for (int h = 0; h < halves; ++h) {
+                const int m = mt * BM + h * HALF_M + quad * 32 + lane;
+                uint16_t *yrow = y + (size_t)m * ldy;
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                uint32_t r[32];
-                tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
-                tc_wait_ld();
-                const int n0 = n_base + ch * 32;
-                if (m < M && n0 < N) {
-                    if (vec_store && n0 + 32 <= N) {
+                for (int ch = 0; ch < BN / 32; ++ch) {
+                    uint32_t r[32];
+                    tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN + ch * 32), r);
+                    tc_wait_ld();
+                    const int n0 = n_base + ch * 32;
+                    if (m < M && n0 < N) {
+                        if (vec_store && n0 + 32 <= N) {
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = pack2_out<BF16>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            o.y = pack2_out<BF16>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            o.z = pack2_out<BF16>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            o.w = pack2_out<BF16>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            *reinterpret_cast<uint4 *>(yrow + n0 + 8 * v) = o;
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 o;
+                                o.x = pack2_out<BF16>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                                o.y = pack2_out<BF16>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                o.z = pack2_out<BF16>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                o.w = pack2_out<BF16>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                *reinterpret_cast<uint4 *>(yrow + n0 + 8 * v) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n0 + j < N) yrow[n0 + j] = (uint16_t)(pack2_out<BF16>(__uint_as_float(r[j]), 0.0f) & 0xFFFF);
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + j < N) yrow[n0 + j] = (uint16_t)(pack2_out<BF16>(__uint_as_float(r[j]), 0.0f) & 0xFFFF);
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty(acc));
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1;
+            if (lane == 0) mbar_arrive(bar_tempty);
+            tphase ^= 1;
         }
     } else {
-        // ---------------- dequantise: packed stage -> swizzled K-major B operand ----------------
+        // ---------------- dequantise: W stage -> swizzled K-major B stage ----------------
         const int dw = warp - FIRST_DEQ_WARP;
         const int g = lane & 7, c = lane >> 3;           // a quarter-warp covers 8 rows of one k-octet
-        int stage = 0;
-        uint32_t phase = 0;
+        RingPos w, b;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            const int nt = t / num_mt;
-            const int valid = min(W_TILES, NT - nt * W_TILES);
-            for (int ks = 0; ks < k_stages; ++ks) {
-                if (!mbar_wait(bar_full(stage), phase, abort_flag, 6)) goto done;
-                const uint8_t *wst = smem + SMEM_W + stage * W_BYTES;
-                uint8_t *bst = smem + SMEM_B + stage * B_BYTES;
+            const int valid = min(W_TILES, NT - (t / num_mt) * W_TILES);
+            for (int ks = 0; ks < k_steps; ++ks) {
+                if (!mbar_wait(bar_full_w(w.s), w.phase, abort_flag, 6)) goto done;
+                if (!mbar_wait(bar_empty_b(b.s), b.phase ^ 1, abort_flag, 8)) goto done;
+                const uint8_t *wst = smem + SMEM_W + w.s * W_BYTES;
+                uint8_t *bst = smem + SMEM_B + b.s * B_BYTES;
 #pragma unroll
                 for (int i = 0; i < W_TILES / NUM_DEQ_WARPS; ++i) {
                     const int tl = dw * (W_TILES / NUM_DEQ_WARPS) + i;
@@ -328,8 +356,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                 }
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_fullb(stage));
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (lane == 0) {
+                    mbar_arrive(bar_full_b(b.s));
+                    mbar_arrive(bar_empty_w(w.s));
+                }
+                w.advance(SW);
+                b.advance(SB);
             }
         }
     }
@@ -342,7 +374,7 @@ done:
         for (int i = 0; i < 64; ++i) __nanosleep(20000);
         __syncthreads();
     }
-    if (warp == 1) {
+    if (warp == WARP_MMA) {
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -405,7 +437,7 @@ extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)gemm::BM};
+    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)gemm::BM};   // 64 k x 256 rows per copy
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&tmap, x_dtype == Q4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                      const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -77,14 +77,25 @@ __device__ __forceinline__ void mma16816_acc(float (&d)[4], uint32_t a0, uint32_
 
 // One ring slot: CHUNK tiles (all of them when FULL, else the first tiles_here).  Every shared
 // memory address is the slot base plus a compile-time offset plus a per-lane constant.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 r;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
+    return r;
+}
+
 template <bool BF16, int MF, int CHUNK, bool FULL>
-__device__ __forceinline__ void consume_slot(const uint8_t *sl, int qoff, int doff, const int (&xoff)[MF],
+__device__ __forceinline__ void consume_slot(uint32_t qaddr, uint32_t daddr, const uint32_t (&xaddr)[MF],
                                              int tiles_here, float (&acc)[MF][4]) {
 #pragma unroll
     for (int t = 0; t < CHUNK; ++t) {
         if (FULL || t < tiles_here) {
-            const uint4 qw = *reinterpret_cast<const uint4 *>(sl + t * TILE_BYTES + qoff);
-            const uint2 dw = *reinterpret_cast<const uint2 *>(sl + t * TILE_BYTES + doff);
+            const uint4 qw = lds128(qaddr + t * TILE_BYTES);
+            const uint2 dw = lds64(daddr + t * TILE_BYTES);
 #pragma unroll
             for (int kbl = 0; kbl < TILE_KB; ++kbl) {
                 uint32_t hlo[4], hhi[4];
@@ -95,7 +106,7 @@ __device__ __forceinline__ void consume_slot(const uint8_t *sl, int qoff, int do
                 const float dhi = __half2float(__ushort_as_half((uint16_t)(dpair >> 16)));
 #pragma unroll
                 for (int f = 0; f < MF; ++f) {
-                    const uint4 xv = *reinterpret_cast<const uint4 *>(sl + xoff[f] + (t * TILE_K + kbl * QK) * 2);
+                    const uint4 xv = lds128(xaddr[f] + (t * TILE_K + kbl * QK) * 2);
                     float part[4];
                     mma16816_first<BF16>(part, hlo[0], hhi[0], hlo[1], hhi[1], xv.x, xv.y);
                     mma16816_acc<BF16>(part, hlo[2], hhi[2], hlo[3], hhi[3], xv.z, xv.w);
@@ -144,29 +155,29 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     const uint8_t *wsrc = prepacked + tile_offset(active ? nt : 0, ku0, KU);
     const int64_t kbase = (int64_t)ku0 * TILE_K;
 
-    // lane 0: arm the slot for the weight bytes and start their copy
-    auto issue_w = [&](int ci, int slot) {
-        const uint32_t bytes = (uint32_t)(min(CHUNK, ntiles - ci * CHUNK) * TILE_BYTES);
-        const uint32_t bar = bar_s + 8u * slot;
-        mbar_expect_tx(bar, bytes);
-        bulk_g2s(ring_s + (uint32_t)(slot * slot_bytes), wsrc + (size_t)ci * G::W_BYTES, bytes, bar);
+    // Refill of ring slot `slot` with chunk `ci`.  Lane 0 arms the slot's barrier with the total
+    // byte count and copies the weights; lanes 0..M-1 copy one activation row slice each.  The
+    // barrier has a single arrival (lane 0's), so it cannot complete before it is armed, however
+    // early the other lanes' copies land.
+    auto chunk_w_bytes = [&](int ci) { return (uint32_t)(min(CHUNK, ntiles - ci * CHUNK) * TILE_BYTES); };
+    auto chunk_x_bytes = [&](int ci) {
+        return (uint32_t)(min((int64_t)CHUNK * TILE_K, K - (kbase + (int64_t)ci * CHUNK * TILE_K)) * 2);
     };
-    // lanes 0..M-1: one activation row slice each (lane 0 arms the barrier for all of them)
-    auto issue_x = [&](int ci, int slot) {
-        const int64_t k0 = kbase + (int64_t)ci * CHUNK * TILE_K;
-        const uint32_t row_bytes = (uint32_t)(min((int64_t)CHUNK * TILE_K, K - k0) * 2);
+    auto issue_w = [&](int ci, int slot) {      // lane 0 only
+        const uint32_t wb = chunk_w_bytes(ci);
         const uint32_t bar = bar_s + 8u * slot;
-        if (lane == 0) mbar_expect_tx(bar, row_bytes * (uint32_t)M);
-        __syncwarp();
-        if (lane < M)
-            bulk_g2s(ring_s + (uint32_t)(slot * slot_bytes + G::W_BYTES + lane * G::X_STRIDE),
-                     x + (size_t)lane * ldx + k0, row_bytes, bar);
+        mbar_expect_tx(bar, wb + chunk_x_bytes(ci) * (uint32_t)M);
+        bulk_g2s(ring_s + (uint32_t)(slot * slot_bytes), wsrc + (size_t)ci * G::W_BYTES, wb, bar);
+    };
+    auto issue_x = [&](int ci, int slot) {      // lanes 0..M-1
+        bulk_g2s(ring_s + (uint32_t)(slot * slot_bytes + G::W_BYTES + lane * G::X_STRIDE),
+                 x + (size_t)lane * ldx + kbase + (int64_t)ci * CHUNK * TILE_K, chunk_x_bytes(ci), bar_s + 8u * slot);
     };
 
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(bar_s + 8u * s) : "memory");   // weights + x
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s + 8u * s) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s)
@@ -185,9 +196,11 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     // dependent launch the weight copies above overlap the previous kernel's tail.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (lane < M) {
 #pragma unroll
-    for (int s = 0; s < SLOTS; ++s)
-        if (s < nchunks) issue_x(s, s);
+        for (int s = 0; s < SLOTS; ++s)
+            if (s < nchunks) issue_x(s, s);
+    }
 
     float acc[MF][4];
 #pragma unroll
@@ -195,13 +208,14 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[f][i] = 0.0f;
 
-    const int qoff = slot_of(g, c) * 16, doff = TILE_QS_BYTES + g * 8;
-    int xoff[MF];
+    // per-lane shared-memory addresses inside slot 0; other slots add a multiple of slot_bytes
+    const uint32_t qaddr0 = ring_s + slot_of(g, c) * 16, daddr0 = ring_s + TILE_QS_BYTES + g * 8;
+    uint32_t xaddr0[MF];
 #pragma unroll
-    for (int f = 0; f < MF; ++f) xoff[f] = G::W_BYTES + min(f * 8 + g, M - 1) * G::X_STRIDE + c * 16;
+    for (int f = 0; f < MF; ++f) xaddr0[f] = ring_s + G::W_BYTES + min(f * 8 + g, M - 1) * G::X_STRIDE + c * 16;
 
     int slot = 0;
-    uint32_t parity = 0;
+    uint32_t parity = 0, soff = 0;           // soff = slot * slot_bytes
     for (int ci = 0; ci < nchunks; ++ci) {
         const uint32_t bar = bar_s + 8u * slot;
         uint32_t done;
@@ -215,16 +229,19 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
             if (!done) atomicCAS(&g_wait_status, 0, 100);
         }
         if (!__all_sync(0xffffffffu, done != 0)) break;
-        const uint8_t *sl = ring + slot * slot_bytes;
+        uint32_t xaddr[MF];
+#pragma unroll
+        for (int f = 0; f < MF; ++f) xaddr[f] = xaddr0[f] + soff;
         const int tiles_here = ntiles - ci * CHUNK;
-        if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(sl, qoff, doff, xoff, CHUNK, acc);
-        else consume_slot<BF16, MF, CHUNK, false>(sl, qoff, doff, xoff, tiles_here, acc);
+        if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(qaddr0 + soff, daddr0 + soff, xaddr, CHUNK, acc);
+        else consume_slot<BF16, MF, CHUNK, false>(qaddr0 + soff, daddr0 + soff, xaddr, tiles_here, acc);
         __syncwarp();                    // every lane has consumed the slot before it is refilled
         if (ci + SLOTS < nchunks) {
             if (lane == 0) issue_w(ci + SLOTS, slot);
-            issue_x(ci + SLOTS, slot);
+            if (lane < M) issue_x(ci + SLOTS, slot);
         }
-        if (++slot == SLOTS) { slot = 0; parity ^= 1; }
+        soff += (uint32_t)slot_bytes;
+        if (++slot == SLOTS) { slot = 0; soff = 0; parity ^= 1; }
     }
 
     // acc[f][0..1] = column g, rows f*8 + 2c, 2c+1 ; acc[f][2..3] = column g+8, same rows
