@@ -8,19 +8,21 @@
 // halves of the tile are two UMMA instructions that share the dequantised B operand, so every
 // weight is dequantised once per 256 rows of X.  Three independent rings in shared memory:
 //   A ring (3 x 32 KB)  warp 0: TMA tile loads of X (256 x 64, 128-byte swizzle)
-//   W ring (4 x 9 KB)   warp 6: bulk copies of the step's packed weights (16 tiles of 576 bytes)
-//   B ring (2 x 32 KB)  warps 7-14 dequantise a W stage into the K-major, 128-byte-swizzled
+//   W ring (4 x 9 KB)   warp 6: bulk copies of the step's packed weights (16 tiles of 576 bytes,
+//                       one per lane)
+//   B ring (2 x 32 KB)  warps 7-14 (two prepacked tiles each) dequantise a W stage into the K-major, 128-byte-swizzled
 //                       bf16/fp16 B operand ((q-8)*d, one rounding) and fence to the async proxy
 //   warp 1      one thread issues tcgen05.mma (kind::f16, M128 N256 K16), 2 halves x 4 per step,
 //               accumulating in TMEM (2 x 256 columns); tcgen05.commit releases A and B stages
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, convert, 16-byte stores; the next
-//               tile's loads and dequantisation run underneath it
+//   warps 2-5, 15-18  epilogue: tcgen05.ld the fp32 accumulators, convert, 16-byte stores; the
+//               next tile's loads and dequantisation run underneath it
 // The W ring is deep because only the dequantisers wait on it; the B ring needs two stages as
 // long as dequantising a stage is faster than its 8 MMAs.
 // Every mbarrier wait is bounded; a wait that gives up records a code in g_gemm_status, raises
 // a CTA-wide abort flag and every role leaves through the common exit that frees TMEM.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "q4b_common.cuh"
@@ -35,9 +37,16 @@ constexpr int A_HALF_BYTES = HALF_M * BK * 2;        // 16384
 constexpr int B_BYTES = BN * BK * 2;                 // 32768
 constexpr int W_TILES = BN / TILE_N;                 // 16 prepacked tiles per step
 constexpr int W_BYTES = W_TILES * TILE_BYTES;        // 9216
-constexpr int NUM_DEQ_WARPS = 8;
+#ifndef Q4B_GEMM_DEQ_WARPS
+#define Q4B_GEMM_DEQ_WARPS 8
+#endif
+#ifndef Q4B_GEMM_WARP_POLL
+#define Q4B_GEMM_WARP_POLL 0
+#endif
+constexpr int NUM_DEQ_WARPS = Q4B_GEMM_DEQ_WARPS;    // prepacked tiles of a step are dealt round-robin to these warps
 constexpr int WARP_A = 0, WARP_MMA = 1, WARP_W = 6, FIRST_DEQ_WARP = 7;   // warps 2..5: epilogue
-constexpr int THREADS = (FIRST_DEQ_WARP + NUM_DEQ_WARPS) * 32;   // 480
+constexpr int FIRST_EPI2_WARP = FIRST_DEQ_WARP + NUM_DEQ_WARPS;   // four more epilogue warps
+constexpr int THREADS = (FIRST_EPI2_WARP + 4) * 32;              // 608
 constexpr int TMEM_COLS = 512;                       // one 256-column fp32 accumulator per half
 constexpr int SMEM_A = 0;
 constexpr int SMEM_B = SMEM_A + SA * A_BYTES;
@@ -49,6 +58,15 @@ constexpr int SMEM_DYN = SMEM_USED + 1024;           // slack to align the base 
 constexpr long long WAIT_LIMIT_CYCLES = 1LL << 28;   // ~0.15 s; far above any legitimate wait
 
 __device__ int g_gemm_status = 0;
+#ifdef Q4B_GEMM_PROFILE
+// development aid: per-CTA cycle counters of where the roles wait (read with cudaMemcpyFromSymbol)
+__device__ long long g_gemm_prof[148 * 8];
+#define PROF_T0() const long long _pt = clock64()
+#define PROF_ADD(slot) prof[slot] += clock64() - _pt
+#else
+#define PROF_T0()
+#define PROF_ADD(slot)
+#endif
 
 // ---- thin PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -69,18 +87,41 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when another role aborted or when this wait itself ran out, in
 // which case it records `code` (first writer wins) and raises the CTA-wide abort flag.
+// The abort flag and the clock are looked at every 64 polls only, and SLEEP_NS > 0 backs the
+// polling off, so that a waiting thread costs few issue slots and little power.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
+    long long t0 = 0;
+    for (int it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort_flag = 1;
-            atomicCAS(&g_gemm_status, 0, code);
-            return false;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+        if ((it & 63) == 0) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(&g_gemm_status, 0, code);
+                return false;
+            }
         }
     }
+}
+// Whole-warp wait with one polling lane: lane 0 polls, the others sleep at the warp barrier and
+// then observe the completed phase themselves with a single try_wait.
+template <int SLEEP_NS = 0>
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code, int lane) {
+#if Q4B_GEMM_WARP_POLL
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait<SLEEP_NS>(bar, parity, abort_flag, code);
+    __syncwarp();
+    if (lane != 0) ok = mbar_try_wait(bar, parity);
+    return __all_sync(0xffffffffu, ok);
+#else
+    (void)lane;
+    return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag, code));
+#endif
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -163,14 +204,13 @@ struct RingPos {
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
-                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store) {
+                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int bn) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    uint8_t *smem = smem_raw + (base - raw);
     const uint32_t bar0 = base + SMEM_BAR;
     auto bar_full_a = [&](int s) { return bar0 + 8u * s; };                          // X tile landed
     auto bar_empty_a = [&](int s) { return bar0 + 8u * (SA + s); };                  // its MMAs retired
@@ -190,7 +230,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         for (int s = 0; s < SW; ++s) { mbar_init(bar_full_w(s), 1); mbar_init(bar_empty_w(s), NUM_DEQ_WARPS); }
         for (int s = 0; s < SB; ++s) { mbar_init(bar_full_b(s), NUM_DEQ_WARPS); mbar_init(bar_empty_b(s), 1); }
         mbar_init(bar_tfull, 1);
-        mbar_init(bar_tempty, 4);
+        mbar_init(bar_tempty, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == WARP_MMA) {
@@ -203,7 +243,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     const uint32_t tmem_base = s_tmem_base;
 
     const int NT = (int)tiles_n(N);                    // prepacked 16-column tiles
-    const int num_mt = (M + BM - 1) / BM, num_nt = (N + BN - 1) / BN;
+    // bn = columns per tile (multiple of 32, at most BN), chosen by the host to even out the waves
+    const int w_tiles = bn / TILE_N;
+    const int num_mt = (M + BM - 1) / BM, num_nt = (N + bn - 1) / bn;
     const int num_tiles = num_mt * num_nt;
     const int k_steps = (K + BK - 1) / BK;
 
@@ -223,36 +265,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         }
     } else if (warp == WARP_W) {
         // ---------------- packed-weight producer ----------------
-        if (lane == 0) {
-            RingPos w;
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-                const int nt0 = (t / num_mt) * W_TILES;
-                const int valid = min(W_TILES, NT - nt0);
-                for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!mbar_wait(bar_empty_w(w.s), w.phase ^ 1, abort_flag, 7)) goto done;
-                    mbar_arrive_expect_tx(bar_full_w(w.s), (uint32_t)(valid * TILE_BYTES));
-                    // the step's column tiles are k_steps tiles apart in the column-tile-major layout
-                    for (int i = 0; i < valid; ++i)
-                        bulk_load(base + SMEM_W + w.s * W_BYTES + i * TILE_BYTES,
-                                  prepacked + tile_offset(nt0 + i, ks, k_steps), TILE_BYTES, bar_full_w(w.s));
-                    w.advance(SW);
-                }
+        // Lane i copies column tile i of the step: sixteen copies issued side by side instead of
+        // one thread working through them (which was slower than the MMAs they feed).
+        RingPos w;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const int nt0 = (t / num_mt) * w_tiles;
+            const int valid = min(w_tiles, NT - nt0);
+            // the step's column tiles are k_steps tiles apart in the column-tile-major layout
+            const uint8_t *src = prepacked + tile_offset(nt0 + min(lane, valid - 1), 0, k_steps);
+            for (int ks = 0; ks < k_steps; ++ks) {
+                if (!mbar_wait_warp(bar_empty_w(w.s), w.phase ^ 1, abort_flag, 7, lane)) goto done;
+                if (lane == 0) mbar_arrive_expect_tx(bar_full_w(w.s), (uint32_t)(valid * TILE_BYTES));
+                __syncwarp();
+                if (lane < valid)
+                    bulk_load(base + SMEM_W + w.s * W_BYTES + lane * TILE_BYTES, src + (size_t)ks * TILE_BYTES, TILE_BYTES,
+                              bar_full_w(w.s));
+                w.advance(SW);
             }
         }
     } else if (warp == WARP_MMA) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BF16, HALF_M, BN);
+            const uint32_t idesc = make_idesc(BF16, HALF_M, bn);
             RingPos a, b;
             uint32_t tphase = 0;
+#ifdef Q4B_GEMM_PROFILE
+            long long prof[4] = {0, 0, 0, 0};
+            const long long prof_start = clock64();
+#endif
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 const int mt = t % num_mt;
                 const int halves = (M - mt * BM > HALF_M) ? 2 : 1;     // skip an all-padding lower half
-                if (!mbar_wait(bar_tempty, tphase ^ 1, abort_flag, 2)) goto done;
+                { PROF_T0(); if (!mbar_wait(bar_tempty, tphase ^ 1, abort_flag, 2)) goto done; PROF_ADD(0); }
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!mbar_wait(bar_full_a(a.s), a.phase, abort_flag, 3)) goto done;
-                    if (!mbar_wait(bar_full_b(b.s), b.phase, abort_flag, 4)) goto done;
+                    { PROF_T0(); if (!mbar_wait(bar_full_a(a.s), a.phase, abort_flag, 3)) goto done; PROF_ADD(1); }
+                    { PROF_T0(); if (!mbar_wait(bar_full_b(b.s), b.phase, abort_flag, 4)) goto done; PROF_ADD(2); }
                     tc_fence_after();
                     const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + b.s * B_BYTES);
                     for (int h = 0; h < halves; ++h) {
@@ -269,22 +317,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                 tc_commit(bar_tfull);
                 tphase ^= 1;
             }
+#ifdef Q4B_GEMM_PROFILE
+            if (blockIdx.x < 148) {
+                g_gemm_prof[blockIdx.x * 8 + 0] = prof[0];
+                g_gemm_prof[blockIdx.x * 8 + 1] = prof[1];
+                g_gemm_prof[blockIdx.x * 8 + 2] = prof[2];
+                g_gemm_prof[blockIdx.x * 8 + 3] = clock64() - prof_start;
+            }
+#endif
         }
-    } else if (warp < WARP_W) {
-        // ---------------- epilogue ----------------
+    } else if (warp < WARP_W || warp >= FIRST_EPI2_WARP) {
+        // ---------------- epilogue: two warps per TMEM lane quadrant, alternate 32-column chunks ----
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
+        const int grp = warp >= FIRST_EPI2_WARP ? 1 : 0;
         uint32_t tphase = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             const int mt = t % num_mt, nt = t / num_mt;
             const int halves = (M - mt * BM > HALF_M) ? 2 : 1;
-            if (!mbar_wait(bar_tfull, tphase, abort_flag, 5)) goto done;
+            if (!mbar_wait_warp<256>(bar_tfull, tphase, abort_flag, 5, lane)) goto done;
             tc_fence_after();
-            const int n_base = nt * BN;
+            const int n_base = nt * bn;
             for (int h = 0; h < halves; ++h) {
                 const int m = mt * BM + h * HALF_M + quad * 32 + lane;
                 uint16_t *yrow = y + (size_t)m * ldy;
 #pragma unroll 1
-                for (int ch = 0; ch < BN / 32; ++ch) {
+                for (int ch = grp; ch < bn / 32; ch += 2) {
                     uint32_t r[32];
                     tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN + ch * 32), r);
                     tc_wait_ld();
@@ -315,43 +372,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         }
     } else {
         // ---------------- dequantise: W stage -> swizzled K-major B stage ----------------
-        const int dw = warp - FIRST_DEQ_WARP;
+        const int dw = warp - FIRST_DEQ_WARP;            // this warp's prepacked tile within the step
         const int g = lane & 7, c = lane >> 3;           // a quarter-warp covers 8 rows of one k-octet
+        // Byte offsets, inside a B stage, of the four 16-byte chunks this lane writes.  Word j of
+        // its slot is block kb = j/2 of row g + 8*(j%2): row (dw*16 + g + 8*(j%2)) of the operand,
+        // chunk (j/2)*4 + c of that row's 128 bytes, XOR-swizzled with the row index modulo 8 (= g).
+        uint32_t boff[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            boff[j] = (uint32_t)((dw * 2 + (j & 1)) * 1024 + g * 128 + ((((j >> 1) * 4 + c) ^ g) << 4));
+        const uint32_t qoff = (uint32_t)(dw * TILE_BYTES + slot_of(g, c) * 16);
+        const uint32_t doff = (uint32_t)(dw * TILE_BYTES + TILE_QS_BYTES + g * 8);
+        constexpr int TILES_PER_WARP = W_TILES / NUM_DEQ_WARPS;      // tile dw + i*NUM_DEQ_WARPS, i < TILES_PER_WARP
         RingPos w, b;
+#ifdef Q4B_GEMM_PROFILE
+        long long prof[4] = {0, 0, 0, 0};
+#endif
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            const int valid = min(W_TILES, NT - (t / num_mt) * W_TILES);
+            const int valid = min(w_tiles, NT - (t / num_mt) * w_tiles);
             for (int ks = 0; ks < k_steps; ++ks) {
-                if (!mbar_wait(bar_full_w(w.s), w.phase, abort_flag, 6)) goto done;
-                if (!mbar_wait(bar_empty_b(b.s), b.phase ^ 1, abort_flag, 8)) goto done;
-                const uint8_t *wst = smem + SMEM_W + w.s * W_BYTES;
-                uint8_t *bst = smem + SMEM_B + b.s * B_BYTES;
+                { PROF_T0(); if (!mbar_wait_warp(bar_full_w(w.s), w.phase, abort_flag, 6, lane)) goto done; PROF_ADD(0); }
+                { PROF_T0(); if (!mbar_wait_warp(bar_empty_b(b.s), b.phase ^ 1, abort_flag, 8, lane)) goto done; PROF_ADD(1); }
+#ifdef Q4B_GEMM_PROFILE
+                const long long _work0 = clock64();
+#endif
 #pragma unroll
-                for (int i = 0; i < W_TILES / NUM_DEQ_WARPS; ++i) {
-                    const int tl = dw * (W_TILES / NUM_DEQ_WARPS) + i;
-                    if (tl < valid) {
-                        const uint4 qw = *reinterpret_cast<const uint4 *>(wst + tl * TILE_BYTES + slot_of(g, c) * 16);
-                        const uint2 dq = *reinterpret_cast<const uint2 *>(wst + tl * TILE_BYTES + TILE_QS_BYTES + g * 8);
-                        const uint32_t words[4] = {qw.x, qw.y, qw.z, qw.w};
-                        const uint16_t dbits[4] = {(uint16_t)(dq.x & 0xFFFF), (uint16_t)(dq.x >> 16),
-                                                   (uint16_t)(dq.y & 0xFFFF), (uint16_t)(dq.y >> 16)};
+                for (int i = 0; i < TILES_PER_WARP; ++i) {
+                    if (dw + i * NUM_DEQ_WARPS >= valid) break;
+                    const uint32_t wst = base + SMEM_W + w.s * W_BYTES + i * NUM_DEQ_WARPS * TILE_BYTES;
+                    const uint32_t bst = base + SMEM_B + b.s * B_BYTES + i * NUM_DEQ_WARPS * 2048;
+                    uint4 qw;
+                    uint2 dq;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(qw.x), "=r"(qw.y), "=r"(qw.z), "=r"(qw.w) : "r"(wst + qoff));
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dq.x), "=r"(dq.y) : "r"(wst + doff));
+                    const uint32_t words[4] = {qw.x, qw.y, qw.z, qw.w};
+                    const uint16_t dbits[4] = {(uint16_t)(dq.x & 0xFFFF), (uint16_t)(dq.x >> 16),
+                                               (uint16_t)(dq.y & 0xFFFF), (uint16_t)(dq.y >> 16)};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            // word j: block (kb = j/2) of row g + 8*(j%2); 8 consecutive k = one 16-byte chunk
-                            const int row = tl * TILE_N + g + 8 * (j & 1);
-                            const int chunk = (j >> 1) * 4 + c;
-                            uint32_t h[4];
-                            dequant_word<BF16>(words[j], h);
-                            const uint32_t d2 = scale_pair<BF16>(dbits[j]);
-                            uint4 o;
-                            if constexpr (BF16) {
-                                o.x = bmul2_bits(h[0], d2); o.y = bmul2_bits(h[1], d2);
-                                o.z = bmul2_bits(h[2], d2); o.w = bmul2_bits(h[3], d2);
-                            } else {
-                                o.x = hmul2_bits(h[0], d2); o.y = hmul2_bits(h[1], d2);
-                                o.z = hmul2_bits(h[2], d2); o.w = hmul2_bits(h[3], d2);
-                            }
-                            *reinterpret_cast<uint4 *>(bst + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4)) = o;
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t h[4];
+                        dequant_word<BF16>(words[j], h);
+                        const uint32_t d2 = scale_pair<BF16>(dbits[j]);
+                        uint4 o;
+                        if constexpr (BF16) {
+                            o.x = bmul2_bits(h[0], d2); o.y = bmul2_bits(h[1], d2);
+                            o.z = bmul2_bits(h[2], d2); o.w = bmul2_bits(h[3], d2);
+                        } else {
+                            o.x = hmul2_bits(h[0], d2); o.y = hmul2_bits(h[1], d2);
+                            o.z = hmul2_bits(h[2], d2); o.w = hmul2_bits(h[3], d2);
                         }
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bst + boff[j]), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
                     }
                 }
                 fence_proxy_async();
@@ -360,10 +430,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                     mbar_arrive(bar_full_b(b.s));
                     mbar_arrive(bar_empty_w(w.s));
                 }
+#ifdef Q4B_GEMM_PROFILE
+                prof[2] += clock64() - _work0;
+#endif
                 w.advance(SW);
                 b.advance(SB);
             }
         }
+#ifdef Q4B_GEMM_PROFILE
+        if (dw == 0 && lane == 0 && blockIdx.x < 148) {
+            g_gemm_prof[blockIdx.x * 8 + 4] = prof[0];
+            g_gemm_prof[blockIdx.x * 8 + 5] = prof[1];
+            g_gemm_prof[blockIdx.x * 8 + 6] = prof[2];
+        }
+#endif
     }
 
 done:
@@ -403,12 +483,23 @@ static EncodeTiledFn get_encode_fn() {
 template <bool BF16>
 static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M, int N, int K, int64_t ldy,
                   int vec_store, int sms, cudaStream_t st) {
+    // Columns per tile: the candidate that needs the least (waves x tile width), with a small
+    // bias towards wide tiles, whose MMAs and X loads are the more efficient.
+    const int mt = (M + BM - 1) / BM;
+    int bn = BN;
+    long best = -1;
+    for (int cand = BN; cand >= 128; cand -= 32) {
+        const long t = (long)mt * ((N + cand - 1) / cand);
+        const long cost = ((t + sms - 1) / sms) * (cand + 24);
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    }
+    if (const char *e = getenv("Q4B_GEMM_BN")) { const int v = atoi(e); if (v >= 32 && v <= BN && v % 32 == 0) bn = v; }
     // per call: the attribute is per device and a process may drive several
     Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int tiles = mt * ((N + bn - 1) / bn);
     const int grid = tiles < sms ? tiles : sms;
     gemm_tcgen05_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K,
-                                                             ldy, vec_store);
+                                                             ldy, vec_store, bn);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }
@@ -450,6 +541,12 @@ extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
                ? gemm::launch<true>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st)
                : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st);
 }
+
+#ifdef Q4B_GEMM_PROFILE
+extern "C" __attribute__((visibility("default"))) int q4b_debug_gemm_profile(long long *out) {
+    return cudaMemcpyFromSymbol(out, gemm::g_gemm_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 6;
+}
+#endif
 
 extern "C" int q4b_wait_status(void *stream, int *detail) {
     Q4B_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
