@@ -57,6 +57,17 @@ int gemv_ksplit_override() {
     return v;
 }
 
+// Q4B_GEMV_GEOM=82|43 forces the decode kernel's ring geometry for M <= 4 (benchmark sweeps only).
+int gemv_geom_override() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("Q4B_GEMV_GEOM");
+        const int k = e ? atoi(e) : 0;
+        v = (k == 82 || k == 43) ? k : 0;
+    }
+    return v;
+}
+
 }  // namespace q4b
 
 using namespace q4b;

@@ -19,6 +19,8 @@
 //
 // Every mbarrier wait is bounded: a wait that gives up sets g_wait_status and the warp stops
 // consuming (its outputs are then wrong, which the status reports) instead of spinning.
+#include <cstdlib>
+
 #include "q4b_common.cuh"
 
 namespace q4b {
@@ -299,12 +301,25 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
 }
 
 // Ring geometry by row count: shared memory per CTA = 8 warps x SLOTS x (CHUNK x 576 + M x row).
-//   M <= 4 : 4 tiles x 3 slots (66..102 KB, 2-3 CTAs per SM)
+//   M <= 4 : 8 tiles x 2 slots or 4 tiles x 3 slots (see below)
 //   M <= 8 : 4 tiles x 2 slots (100 KB)          M <= 16 : 2 tiles x 2 slots (98 KB)
+int device_sm_count();
+int gemv_geom_override();
+
 template <bool BF16, int KS>
 static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
                          int64_t ldy, int flags, cudaStream_t st) {
-    if (M <= 4) return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    if (M <= 4) {
+        // 8 tiles x 2 slots keeps more bytes in flight per warp (2 CTAs per SM); 4 tiles x 3 slots
+        // fits 3 CTAs per SM, which wins when warps are short (<= 8 tiles) and the grid is several
+        // waves of CTAs.
+        const int64_t grid = ceil_div(tiles_n(N), GEMV_WARPS / KS);
+        const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
+        int geom = (tiles_per_warp <= 8 && grid > 2LL * device_sm_count()) ? 43 : 82;
+        if (const int o = gemv_geom_override()) geom = o;
+        if (geom == 82) return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    }
     if (M <= 8) return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
     return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
 }
