@@ -57,13 +57,14 @@ int gemv_ksplit_override() {
     return v;
 }
 
-// Q4B_GEMV_GEOM=82|43 forces the decode kernel's ring geometry for M <= 4 (benchmark sweeps only).
+// Q4B_GEMV_GEOM=<tiles per slot><slots> (82, 83, 43, 42, 44) forces the decode kernel's ring
+// geometry for M = 1 (benchmark sweeps only).
 int gemv_geom_override() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("Q4B_GEMV_GEOM");
         const int k = e ? atoi(e) : 0;
-        v = (k == 82 || k == 43) ? k : 0;
+        v = (k == 82 || k == 43 || k == 42 || k == 44 || k == 83) ? k : 0;
     }
     return v;
 }

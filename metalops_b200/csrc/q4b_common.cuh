@@ -112,6 +112,25 @@ __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t (&h)[4]) {
     }
 }
 
+// The same without the subtraction: pair s holds (OFF + q) with OFF = 1024 for pairs 0 and 2 and
+// 64 for pairs 1 and 3 (fp16), or 128 for every pair (bf16).  The single-row decode kernel
+// removes sum((OFF + 8) * x) once per 32-k block instead of subtracting per pair.
+template <bool BF16>
+__device__ __forceinline__ void dequant_word_biased(uint32_t w, uint32_t (&h)[4]) {
+    if constexpr (!BF16) {
+        const uint32_t w8 = w >> 8;
+        h[0] = lop3_and_or(w, 0x000F000Fu, 0x64006400u);
+        h[1] = lop3_and_or(w, 0x00F000F0u, 0x54005400u);
+        h[2] = lop3_and_or(w8, 0x000F000Fu, 0x64006400u);
+        h[3] = lop3_and_or(w8, 0x00F000F0u, 0x54005400u);
+    } else {
+        h[0] = lop3_and_or(w, 0x000F000Fu, 0x43004300u);
+        h[1] = lop3_and_or(w >> 4, 0x000F000Fu, 0x43004300u);
+        h[2] = lop3_and_or(w >> 8, 0x000F000Fu, 0x43004300u);
+        h[3] = lop3_and_or(w >> 12, 0x000F000Fu, 0x43004300u);
+    }
+}
+
 // ---- host-side helpers ---------------------------------------------------------------
 void set_cuda_error(cudaError_t e);
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }

@@ -122,6 +122,85 @@ __device__ __forceinline__ void consume_slot(uint32_t qaddr, uint32_t daddr, con
     }
 }
 
+// Single activation row (M = 1).  With one row, seven of the eight mma columns would carry
+// nothing, so the columns are given to eight different 32-k blocks instead: a group of four
+// tiles (eight blocks) shares one accumulator, lane (g, c) feeding x only into column g while it
+// multiplies block g (every other lane reads a page of zeros), so that accumulator column j ends
+// up holding block j's partial product.  That leaves one scale fma per tile instead of eight,
+// and lets the nibbles go in biased, as (OFF + q): the accumulator starts at
+// -sum((OFF + 8) * x) of the column's block, computed once per block from the x the lane holds
+// anyway, so no per-pair subtraction is needed.
+//   qaddr  lane's nibble slot in tile 0 of the ring slot
+//   dsel   scales of tile c of group 0 (the lane's accumulator columns 2c, 2c+1 are that tile's blocks)
+//   xsel   per block j of a group: the x slice (+ c*16) if j == g, else the zero page (+ c*16)
+//   xown   x of the lane's own block in group 0: slice + ((g/2)*64 + (g%2)*32 + c*8) elements
+template <bool BF16, int CHUNK, bool FULL>
+__device__ __forceinline__ void consume_slot_m1(uint32_t qaddr, uint32_t dsel, const uint32_t (&xsel)[8], uint32_t xown,
+                                                int c, int tiles_here, float (&acc)[2]) {
+    static_assert(CHUNK % 4 == 0, "groups of four tiles");
+    constexpr int NG = CHUNK / 4;
+    constexpr float CL = BF16 ? 136.0f : 1032.0f;      // k offsets 0,1,4,5 of a nibble word
+    constexpr float CH = BF16 ? 136.0f : 72.0f;        // k offsets 2,3,6,7
+    float part[NG][4];
+    bool col_ok[NG];
+    // accumulators start at -sum((OFF + 8) * x) of their block: each lane sums its own 8 k of
+    // block g, the quad adds up, and the lanes owning columns 2c, 2c+1 fetch the two totals
+#pragma unroll
+    for (int grp = 0; grp < NG; ++grp) {
+        const uint4 xo = lds128(xown + grp * 4 * TILE_K * 2);
+        float2 p0, p1, p2, p3;
+        if constexpr (BF16) {
+            p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.x));
+            p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.y));
+            p2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.z));
+            p3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.w));
+        } else {
+            p0 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.x));
+            p1 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.y));
+            p2 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.z));
+            p3 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.w));
+        }
+        float s = CL * ((p0.x + p0.y) + (p2.x + p2.y)) + CH * ((p1.x + p1.y) + (p3.x + p3.y));
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        float c0 = -__shfl_sync(0xffffffffu, s, 8 * c);          // block 2c   lives in quad g = 2c
+        float c1 = -__shfl_sync(0xffffffffu, s, 8 * c + 4);      // block 2c+1 lives in quad g = 2c+1
+        col_ok[grp] = FULL || (grp * 4 + c) < tiles_here;        // tile c of the group exists
+        if (!col_ok[grp]) { c0 = 0.0f; c1 = 0.0f; }
+        part[grp][0] = c0; part[grp][1] = c1; part[grp][2] = c0; part[grp][3] = c1;
+    }
+    // the groups' accumulator chains are independent: step them side by side
+#pragma unroll
+    for (int t4 = 0; t4 < 4; ++t4) {
+#pragma unroll
+        for (int grp = 0; grp < NG; ++grp) {
+            const int t = grp * 4 + t4;
+            if (FULL || t < tiles_here) {
+                const uint4 qw = lds128(qaddr + t * TILE_BYTES);
+#pragma unroll
+                for (int kbl = 0; kbl < TILE_KB; ++kbl) {
+                    const uint4 xv = lds128(xsel[t4 * 2 + kbl] + (t * TILE_K + kbl * QK) * 2);
+                    uint32_t hlo[4], hhi[4];
+                    dequant_word_biased<BF16>(kbl ? qw.z : qw.x, hlo);     // column g
+                    dequant_word_biased<BF16>(kbl ? qw.w : qw.y, hhi);     // column g + 8
+                    mma16816_acc<BF16>(part[grp], hlo[0], hhi[0], hlo[1], hhi[1], xv.x, xv.y);
+                    mma16816_acc<BF16>(part[grp], hlo[2], hhi[2], hlo[3], hhi[3], xv.z, xv.w);
+                }
+            }
+        }
+    }
+    // part[.][0], [1]: output column g, blocks kb0, kb1 of tile c; [2], [3]: column g+8
+#pragma unroll
+    for (int grp = 0; grp < NG; ++grp) {
+        uint2 dq = make_uint2(0u, 0u);
+        if (col_ok[grp]) dq = lds64(dsel + grp * 4 * TILE_BYTES);
+        const float2 d0 = __half22float2(*reinterpret_cast<const __half2 *>(&dq.x));   // d(kb0, g), d(kb0, g+8)
+        const float2 d1 = __half22float2(*reinterpret_cast<const __half2 *>(&dq.y));   // d(kb1, g), d(kb1, g+8)
+        acc[0] = fmaf(d0.x, part[grp][0], fmaf(d1.x, part[grp][1], acc[0]));
+        acc[1] = fmaf(d0.y, part[grp][2], fmaf(d1.y, part[grp][3], acc[1]));
+    }
+}
+
 template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
     if constexpr (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
     else return __half_as_ushort(__float2half_rn(v));
@@ -129,7 +208,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
 
 // KS = warps of a CTA that split k for the same column tile; the CTA covers 8/KS column tiles.
 // CHUNK tiles per ring slot, SLOTS slots per warp.
-template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
+template <bool BF16, int MF, bool M1, int KS, int CHUNK, int SLOTS>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *__restrict__ prepacked, int64_t K,
             int64_t N, uint16_t *__restrict__ y, int64_t ldy) {
@@ -138,7 +217,13 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     extern __shared__ __align__(128) uint8_t ring_all[];
     __shared__ __align__(8) uint64_t bars[GEMV_WARPS][SLOTS];
     __shared__ float red[GEMV_WARPS][MF][TILE_N * 8];
+    __shared__ __align__(16) uint8_t zero_page[M1 ? G::X_ROW + 64 : 16];    // what the other seven mma columns read
 
+    if constexpr (M1) {
+        for (int i = threadIdx.x * 16; i < (int)sizeof(zero_page); i += GEMV_THREADS * 16)
+            *reinterpret_cast<uint4 *>(zero_page + i) = make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads();
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int ks = warp % KS, ntl = warp / KS;
@@ -215,6 +300,12 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     uint32_t xaddr0[MF];
 #pragma unroll
     for (int f = 0; f < MF; ++f) xaddr0[f] = ring_s + G::W_BYTES + min(f * 8 + g, M - 1) * G::X_STRIDE + c * 16;
+    // single-row path: see consume_slot_m1
+    float acc1[2] = {0.0f, 0.0f};
+    const uint32_t zero_s = smem_addr_u32(zero_page) + c * 16;
+    const uint32_t xslice0 = ring_s + G::W_BYTES + c * 16;
+    const uint32_t xown0 = ring_s + G::W_BYTES + ((g >> 1) * TILE_K + (g & 1) * QK + c * 8) * 2;
+    const uint32_t dsel0 = ring_s + c * TILE_BYTES + TILE_QS_BYTES + g * 8;
 
     int slot = 0;
     uint32_t parity = 0, soff = 0;           // soff = slot * slot_bytes
@@ -235,8 +326,18 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 #pragma unroll
         for (int f = 0; f < MF; ++f) xaddr[f] = xaddr0[f] + soff;
         const int tiles_here = ntiles - ci * CHUNK;
-        if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(qaddr0 + soff, daddr0 + soff, xaddr, CHUNK, acc);
-        else consume_slot<BF16, MF, CHUNK, false>(qaddr0 + soff, daddr0 + soff, xaddr, tiles_here, acc);
+        if constexpr (M1) {
+            uint32_t xsel[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xsel[j] = (g == j) ? xslice0 + soff : zero_s;
+            if (tiles_here >= CHUNK)
+                consume_slot_m1<BF16, CHUNK, true>(qaddr0 + soff, dsel0 + soff, xsel, xown0 + soff, c, CHUNK, acc1);
+            else
+                consume_slot_m1<BF16, CHUNK, false>(qaddr0 + soff, dsel0 + soff, xsel, xown0 + soff, c, tiles_here, acc1);
+        } else {
+            if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(qaddr0 + soff, daddr0 + soff, xaddr, CHUNK, acc);
+            else consume_slot<BF16, MF, CHUNK, false>(qaddr0 + soff, daddr0 + soff, xaddr, tiles_here, acc);
+        }
         __syncwarp();                    // every lane has consumed the slot before it is refilled
         if (ci + SLOTS < nchunks) {
             if (lane == 0) issue_w(ci + SLOTS, slot);
@@ -246,9 +347,21 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
         if (++slot == SLOTS) { slot = 0; soff = 0; parity ^= 1; }
     }
 
+    if constexpr (M1) {
+        // each lane of a quad summed different blocks of output columns g and g+8
+        float a0 = acc1[0], a1 = acc1[1];
+        a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
+        a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+        a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
+        a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+        if (c == 0) {
+            red[warp][0][g] = a0;
+            red[warp][0][g + 8] = a1;
+        }
+    }
     // acc[f][0..1] = column g, rows f*8 + 2c, 2c+1 ; acc[f][2..3] = column g+8, same rows
 #pragma unroll
-    for (int f = 0; f < MF; ++f) {
+    for (int f = 0; f < (M1 ? 0 : MF); ++f) {
         red[warp][f][(2 * c) * TILE_N + g] = acc[f][0];
         red[warp][f][(2 * c + 1) * TILE_N + g] = acc[f][1];
         red[warp][f][(2 * c) * TILE_N + g + 8] = acc[f][2];
@@ -270,7 +383,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     }
 }
 
-template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
+template <bool BF16, int MF, bool M1, int KS, int CHUNK, int SLOTS>
 static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
                        int64_t ldy, int flags, cudaStream_t st) {
     constexpr int NTC = GEMV_WARPS / KS;
@@ -280,7 +393,7 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>,
+        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, M1, KS, CHUNK, SLOTS>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(MF * 8)));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
@@ -295,7 +408,7 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
-    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, M1, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
                                     (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy));
     return Q4B_OK;
 }
@@ -309,6 +422,22 @@ int gemv_geom_override();
 template <bool BF16, int KS>
 static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
                          int64_t ldy, int flags, cudaStream_t st) {
+    if (M == 1) {
+        // one row: the eight mma columns carry eight 32-k blocks (see consume_slot_m1)
+        switch (gemv_geom_override()) {
+            case 43: return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            case 42: return launch_gemv<BF16, 1, true, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            case 44: return launch_gemv<BF16, 1, true, KS, 4, 4>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            case 82: return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            case 83: return launch_gemv<BF16, 1, true, KS, 8, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            default: break;
+        }
+        const int64_t grid = ceil_div(tiles_n(N), GEMV_WARPS / KS);
+        const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
+        if (tiles_per_warp <= 8 && grid > 2LL * device_sm_count())
+            return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    }
     if (M <= 4) {
         // 8 tiles x 2 slots keeps more bytes in flight per warp (2 CTAs per SM); 4 tiles x 3 slots
         // fits 3 CTAs per SM, which wins when warps are short (<= 8 tiles) and the grid is several
@@ -317,11 +446,11 @@ static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacke
         const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
         int geom = (tiles_per_warp <= 8 && grid > 2LL * device_sm_count()) ? 43 : 82;
         if (const int o = gemv_geom_override()) geom = o;
-        if (geom == 82) return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        if (geom == 82) return launch_gemv<BF16, 1, false, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        return launch_gemv<BF16, 1, false, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
     }
-    if (M <= 8) return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-    return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    if (M <= 8) return launch_gemv<BF16, 1, false, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    return launch_gemv<BF16, 2, false, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
 }
 
 template <bool BF16>
