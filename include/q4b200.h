@@ -125,6 +125,52 @@ Q4B_API int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const
                int64_t K, int64_t N, void *y, int64_t ldy, int flags, void *stream);
 
 /*
+ * The same products with an optional fp32 term added before the single rounding to the output
+ * dtype: Y = round(X . dequant(W) + addend), addend [M, N] fp32 with leading dimension ld_add
+ * (NULL = none).  Used for the group-wise format's zero-point term and for a fused bias
+ * (the reference adds its bias after the matmul, quantization.py:602-603).
+ */
+Q4B_API int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+                            int64_t K, int64_t N, const float *addend, int64_t ld_add, void *y,
+                            int64_t ldy, int flags, void *stream);
+Q4B_API int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+                            int64_t K, int64_t N, const float *addend, int64_t ld_add, void *y,
+                            int64_t ldy, int flags, void *stream);
+Q4B_API int q4b_matmul_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
+                              const void *prepacked, int64_t K, int64_t N, const float *addend,
+                              int64_t ld_add, void *y, int64_t ldy, int flags, void *stream);
+
+/*
+ * Group-wise asymmetric INT4 format of the reference (quantization.py:26-239; its Metal
+ * quantizer quantize_to_int4, quant_kernels.metal:634-690 / core_mps.mm:4655-4705, and matmul
+ * dispatcher matmul_int4_metal, core_mps.mm:5612-5776):
+ *   packed uint8 [K/2, N] (byte r of column n = q[2r] | q[2r+1] << 4), scales and zeros
+ *   [ceil(K/group), N] in the weight's dtype, W = (q - zero) * scale.
+ *
+ * q4b_int4g_quantize    bit-exact with quantize_int4: per (group, column) min/max,
+ *                       scale = max((max-min)/15, 1e-8), zero = -min/scale,
+ *                       q = clamp(round(w/scale + zero), 0, 15), every step rounded in w's dtype.
+ *                       K and group even.  scales/zeros are written in w's dtype.
+ * q4b_int4g_dequantize  ((q - zero) * scale) in fp32, cast to out_dtype (dequantize_int4).
+ * q4b_int4g_prepack     converts to the streaming tile layout used by the matmul kernels
+ *                       (block scale d = fp16(scale), needs group % 32 == 0 and K % 32 == 0) and
+ *                       writes corr [ceil(K/group), N] fp32 = 8*d - zero*scale, the per-group
+ *                       constant that the symmetric tiles leave out.
+ * q4b_int4g_addend      addend[m, n] = sum_g corr[g, n] * sum_{k in g} x[m, k]  (fp32 [M, N]),
+ *                       to be passed to q4b_matmul_addend with the prepacked tiles.
+ */
+Q4B_API int q4b_int4g_quantize(const void *w, int w_dtype, int64_t K, int64_t N, int64_t group,
+                               void *packed_out, void *scales_out, void *zeros_out, void *stream);
+Q4B_API int q4b_int4g_dequantize(const void *packed, const void *scales, const void *zeros,
+                                 int sz_dtype, int64_t K, int64_t N, int64_t group, void *w_out,
+                                 int out_dtype, void *stream);
+Q4B_API int q4b_int4g_prepack(const void *packed, const void *scales, const void *zeros,
+                              int sz_dtype, int64_t K, int64_t N, int64_t group,
+                              void *prepacked_out, float *corr_out, void *stream);
+Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr,
+                             int64_t K, int64_t N, int64_t group, float *addend_out, void *stream);
+
+/*
  * The matmul kernels bound every mbarrier wait; a wait that gives up makes the kernel set a
  * status word on the device and stop early (its output is then incomplete).  This call
  * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with

@@ -13,6 +13,7 @@ from .quantization import (  # noqa: E402
     BLOCK_Q4_0_SIZE,
     QK4_0,
     Int4Linear,
+    Q4Linear,
     Q4Prepacked,
     dequantize_ggml_q4_0,
     dequantize_int4,
@@ -20,6 +21,7 @@ from .quantization import (  # noqa: E402
     matmul_int4,
     matmul_int8,
     prepack_ggml_q4_0,
+    prepack_int4,
     quantize_ggml_q4_0,
     quantize_int4,
     unpack_ggml_q4_0,
@@ -38,7 +40,7 @@ def has_native_kernels() -> bool:
 
 __all__ = [
     "quantize_ggml_q4_0", "dequantize_ggml_q4_0", "matmul_ggml_q4_0", "prepack_ggml_q4_0",
-    "unpack_ggml_q4_0", "Q4Prepacked", "Int4Linear", "quantize_int4", "dequantize_int4", "matmul_int4",
+    "unpack_ggml_q4_0", "Q4Prepacked", "Int4Linear", "Q4Linear", "prepack_int4", "quantize_int4", "dequantize_int4", "matmul_int4",
     "matmul_int8", "ColumnParallelQ4Linear", "shard_bounds", "has_native_kernels", "QK4_0",
     "BLOCK_Q4_0_SIZE",
 ]

@@ -105,8 +105,15 @@ extern "C" int q4b_device_ok(void) {
 
 extern "C" int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                           int64_t N, void *y, int64_t ldy, int flags, void *stream) {
-    if (M >= 1 && M <= 16) return q4b_gemv(x, x_dtype, M, ldx, prepacked, K, N, y, ldy, flags, stream);
-    return q4b_gemm(x, x_dtype, M, ldx, prepacked, K, N, y, ldy, flags, stream);
+    return q4b_matmul_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y, ldy, flags, stream);
+}
+
+extern "C" int q4b_matmul_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                                 int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
+                                 void *stream) {
+    if (M >= 1 && M <= 16)
+        return q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, stream);
+    return q4b_gemm_addend(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, stream);
 }
 
 extern "C" int q4b_matmul_host(const void *x_host, void *x_dev, int x_dtype, int64_t M, const void *prepacked,

@@ -204,7 +204,8 @@ struct RingPos {
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
-                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int bn) {
+                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int bn,
+                    const float *__restrict__ addend, int64_t ld_add) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -346,6 +347,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                     tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN + ch * 32), r);
                     tc_wait_ld();
                     const int n0 = n_base + ch * 32;
+                    if (addend != nullptr && m < M) {            // fp32 term added before the one rounding
+                        const float *arow = addend + (size_t)m * ld_add + n0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + arow[j]);
+                    }
                     if (m < M && n0 < N) {
                         if (vec_store && n0 + 32 <= N) {
 #pragma unroll
@@ -482,7 +489,7 @@ static EncodeTiledFn get_encode_fn() {
 
 template <bool BF16>
 static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M, int N, int K, int64_t ldy,
-                  int vec_store, int sms, cudaStream_t st) {
+                  int vec_store, int sms, const float *addend, int64_t ld_add, cudaStream_t st) {
     // Columns per tile: the candidate that needs the least (waves x tile width), with a small
     // bias towards wide tiles, whose MMAs and X loads are the more efficient.
     const int mt = (M + BM - 1) / BM;
@@ -499,7 +506,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
     const int tiles = mt * ((N + bn - 1) / bn);
     const int grid = tiles < sms ? tiles : sms;
     gemm_tcgen05_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K,
-                                                             ldy, vec_store, bn);
+                                                             ldy, vec_store, bn, addend, ld_add);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }
@@ -515,7 +522,14 @@ using namespace q4b;
 
 extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                         int64_t N, void *y, int64_t ldy, int flags, void *stream) {
+    return q4b_gemm_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y, ldy, flags, stream);
+}
+
+extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                               int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
+                               void *stream) {
     (void)flags;
+    if (addend != nullptr && ld_add < N) return Q4B_ERR_ARG;
     if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
     if (K % QK || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return Q4B_ERR_SHAPE;
@@ -538,8 +552,8 @@ extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
     const int sms = device_sm_count();
     cudaStream_t st = (cudaStream_t)stream;
     return x_dtype == Q4B_BF16
-               ? gemm::launch<true>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st)
-               : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, st);
+               ? gemm::launch<true>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, addend, ld_add, st)
+               : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, addend, ld_add, st);
 }
 
 #ifdef Q4B_GEMM_PROFILE

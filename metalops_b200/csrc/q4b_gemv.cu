@@ -211,7 +211,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
 template <bool BF16, int MF, bool M1, int KS, int CHUNK, int SLOTS>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *__restrict__ prepacked, int64_t K,
-            int64_t N, uint16_t *__restrict__ y, int64_t ldy) {
+            int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add) {
     using G = SlotGeom<CHUNK>;
     constexpr int NTC = GEMV_WARPS / KS;
     extern __shared__ __align__(128) uint8_t ring_all[];
@@ -378,6 +378,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
             float s = 0.0f;
 #pragma unroll
             for (int j = 0; j < KS; ++j) s += red[tl * KS + j][f][m8 * TILE_N + nl];
+            if (addend != nullptr) s += addend[(size_t)m * ld_add + n];     // fp32 term added before the one rounding
             y[(size_t)m * ldy + n] = out_bits<BF16>(s);
         }
     }
@@ -385,7 +386,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 
 template <bool BF16, int MF, bool M1, int KS, int CHUNK, int SLOTS>
 static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
-                       int64_t ldy, int flags, cudaStream_t st) {
+                       int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
     constexpr int NTC = GEMV_WARPS / KS;
     const int smem = GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(M);
     // opt in to > 48 KB of dynamic shared memory once per device and instantiation
@@ -409,7 +410,7 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, M1, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy));
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add));
     return Q4B_OK;
 }
 
@@ -421,22 +422,22 @@ int gemv_geom_override();
 
 template <bool BF16, int KS>
 static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
-                         int64_t ldy, int flags, cudaStream_t st) {
+                         int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
     if (M == 1) {
         // one row: the eight mma columns carry eight 32-k blocks (see consume_slot_m1)
         switch (gemv_geom_override()) {
-            case 43: return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-            case 42: return launch_gemv<BF16, 1, true, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-            case 44: return launch_gemv<BF16, 1, true, KS, 4, 4>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-            case 82: return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-            case 83: return launch_gemv<BF16, 1, true, KS, 8, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            case 43: return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 42: return launch_gemv<BF16, 1, true, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 44: return launch_gemv<BF16, 1, true, KS, 4, 4>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 82: return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 83: return launch_gemv<BF16, 1, true, KS, 8, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
             default: break;
         }
         const int64_t grid = ceil_div(tiles_n(N), GEMV_WARPS / KS);
         const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
         if (tiles_per_warp <= 8 && grid > 2LL * device_sm_count())
-            return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+            return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
     }
     if (M <= 4) {
         // 8 tiles x 2 slots keeps more bytes in flight per warp (2 CTAs per SM); 4 tiles x 3 slots
@@ -446,21 +447,21 @@ static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacke
         const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
         int geom = (tiles_per_warp <= 8 && grid > 2LL * device_sm_count()) ? 43 : 82;
         if (const int o = gemv_geom_override()) geom = o;
-        if (geom == 82) return launch_gemv<BF16, 1, false, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        return launch_gemv<BF16, 1, false, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        if (geom == 82) return launch_gemv<BF16, 1, false, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        return launch_gemv<BF16, 1, false, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
     }
-    if (M <= 8) return launch_gemv<BF16, 1, false, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-    return launch_gemv<BF16, 2, false, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+    if (M <= 8) return launch_gemv<BF16, 1, false, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    return launch_gemv<BF16, 2, false, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
 }
 
 template <bool BF16>
 static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
-                          void *y, int64_t ldy, int flags, cudaStream_t st) {
+                          void *y, int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
     switch (ksplit) {
-        case 8: return launch_gemv_m<BF16, 8>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        case 4: return launch_gemv_m<BF16, 4>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        case 2: return launch_gemv_m<BF16, 2>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
-        default: return launch_gemv_m<BF16, 1>(x, M, ldx, prepacked, K, N, y, ldy, flags, st);
+        case 8: return launch_gemv_m<BF16, 8>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        case 4: return launch_gemv_m<BF16, 4>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        case 2: return launch_gemv_m<BF16, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        default: return launch_gemv_m<BF16, 1>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
     }
 }
 
@@ -485,6 +486,13 @@ using namespace q4b;
 
 extern "C" int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                         int64_t N, void *y, int64_t ldy, int flags, void *stream) {
+    return q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y, ldy, flags, stream);
+}
+
+extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                               int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
+                               void *stream) {
+    if (addend != nullptr && ld_add < N) return Q4B_ERR_ARG;
     if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
     if (M > 16 || K % QK || tiles_k(K) > (1 << 24)) return Q4B_ERR_SHAPE;
@@ -500,6 +508,6 @@ extern "C" int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
     }
     while (ks > 1 && KU < ks) ks /= 2;
     cudaStream_t st = (cudaStream_t)stream;
-    return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st)
-                               : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, flags, st);
+    return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st)
+                               : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
 }

@@ -1,0 +1,264 @@
+// Group-wise asymmetric INT4 format of the reference: quantize, dequantize, and the conversion
+// that lets the q4_0 matmul kernels serve it.
+//
+// Reference: quantize_int4 / dequantize_int4 / matmul_int4 in
+// packages/metalcore/src/metalcore/quantization.py:26-239, the Metal quantizer quantize_to_int4
+// (quant_kernels.metal:634-690, core_mps.mm:4655-4705) and dispatcher matmul_int4_metal
+// (core_mps.mm:5612-5776).  W = (q - zero) * scale with one (scale, zero) per `group` rows of k
+// and column; weight_packed [K/2, N] holds k = 2r in the low and 2r+1 in the high nibble.
+//
+// How the matmul is served: (q - zero) * scale = (q - 8) * d + [q * (scale - d) + 8 * d - zero * scale]
+// with d = fp16(scale).  The first term is exactly what the q4_0 tiles compute; the bracket is
+// replaced by its q-independent part corr = 8 * d - zero * scale (dropping q * (scale - d), a
+// relative weight error of at most 2^-12), which contributes corr[g, n] * sum_{k in g} x[m, k]:
+// a small fp32 [M, N] addend that the matmul kernels add before their single rounding.
+#include "q4b_common.cuh"
+
+namespace q4b {
+
+template <typename T> struct Num;
+template <> struct Num<float> {
+    static __device__ __forceinline__ float r(float v) { return v; }
+    static __device__ __forceinline__ float ld(const float *p) { return __ldg(p); }
+    static __device__ __forceinline__ void st(float *p, float v) { *p = v; }
+};
+template <> struct Num<__half> {
+    static __device__ __forceinline__ float r(float v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ float ld(const __half *p) { return __half2float(__ldg(p)); }
+    static __device__ __forceinline__ void st(__half *p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct Num<__nv_bfloat16> {
+    static __device__ __forceinline__ float r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ float ld(const __nv_bfloat16 *p) { return __bfloat162float(__ldg(p)); }
+    static __device__ __forceinline__ void st(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// One thread per (group, column).  Every arithmetic step is rounded to the weight's dtype, as
+// the reference's separate torch ops do (quantization.py:69-83).
+template <typename T>
+__global__ void __launch_bounds__(128)
+int4g_quantize_kernel(const T *__restrict__ w, int64_t K, int64_t N, int64_t group, uint8_t *__restrict__ packed,
+                      T *__restrict__ scales, T *__restrict__ zeros) {
+    const int64_t n = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    const int64_t g = blockIdx.y;
+    if (n >= N) return;
+    const int64_t k0 = g * group, k1 = min(k0 + group, K);
+    float lo = INFINITY, hi = -INFINITY;
+    bool nan = false;
+    for (int64_t k = k0; k < k1; ++k) {
+        const float v = Num<T>::ld(w + k * N + n);
+        nan |= (v != v);
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
+    }
+    if (nan) { lo = NAN; hi = NAN; }                                        // torch min/max propagate NaN
+    float scale = Num<T>::r(__fdiv_rn(Num<T>::r(__fsub_rn(hi, lo)), 15.0f));   // quantization.py:74
+    const float tiny = Num<T>::r(1e-8f);                                     // clamp(min=1e-8) in T: 0 for fp16
+    if (scale < tiny) scale = tiny;                                          // quantization.py:75 (NaN stays NaN)
+    const float zero = Num<T>::r(__fdiv_rn(-lo, scale));                     // quantization.py:76
+    Num<T>::st(scales + g * N + n, scale);
+    Num<T>::st(zeros + g * N + n, zero);
+    auto quant = [&](int64_t k) -> uint32_t {
+        float t = Num<T>::r(__fdiv_rn(Num<T>::ld(w + k * N + n), scale));    // quantization.py:83, op by op
+        t = Num<T>::r(__fadd_rn(t, zero));
+        t = fminf(fmaxf(rintf(t), 0.0f), 15.0f);                             // NaN -> 0
+        return (uint32_t)t;
+    };
+    for (int64_t k = k0; k + 1 < k1; k += 2)                                // group and K are even
+        packed[(k >> 1) * N + n] = (uint8_t)(quant(k) | (quant(k + 1) << 4));
+}
+
+// ((q - zero) * scale) in fp32, then cast (quantization.py:131-153).  One thread per packed byte.
+template <typename TS, typename TO>
+__global__ void __launch_bounds__(128)
+int4g_dequantize_kernel(const uint8_t *__restrict__ packed, const TS *__restrict__ scales, const TS *__restrict__ zeros,
+                        int64_t K, int64_t N, int64_t group, TO *__restrict__ w) {
+    const int64_t n = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    const int64_t r = blockIdx.y;
+    if (n >= N) return;
+    const uint32_t b = packed[r * N + n];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int64_t k = 2 * r + i;
+        const int64_t g = k / group;
+        const float q = (float)((b >> (4 * i)) & 0xF);
+        const float v = __fmul_rn(__fsub_rn(q, Num<TS>::ld(zeros + g * N + n)), Num<TS>::ld(scales + g * N + n));
+        Num<TO>::st(w + k * N + n, v);
+    }
+}
+
+// packed [K/2, N] + scales -> streaming tiles with block scale d = fp16(scale).  One warp per tile.
+template <typename TS>
+__global__ void __launch_bounds__(128)
+int4g_prepack_kernel(const uint8_t *__restrict__ packed, const TS *__restrict__ scales, int64_t K, int64_t N,
+                     int64_t group, uint8_t *__restrict__ prepacked) {
+    const int64_t KB = K / QK, NT = tiles_n(N), KU = tiles_k(K);
+    const int64_t tile_id = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (tile_id >= NT * KU) return;
+    const int64_t nt = tile_id / KU, ku = tile_id % KU;
+    const int p = threadIdx.x & 31;
+    int g, c;
+    slot_inverse(p, g, c);
+    uint32_t wds[4];
+    uint16_t ds[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t kb = ku * TILE_KB + (j >> 1);
+        const int64_t n = nt * TILE_N + g + 8 * (j & 1);
+        wds[j] = 0x88888888u;
+        ds[j] = 0;
+        if (kb < KB && n < N) {
+            const int64_t r0 = kb * (QK / 2) + 4 * c;          // packed rows of k = kb*32 + 8c .. +7
+            uint32_t iw = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) iw |= (uint32_t)packed[(r0 + i) * N + n] << (8 * i);
+            wds[j] = interchange_to_prepacked_word(iw);
+            ds[j] = __half_as_ushort(__float2half_rn(Num<TS>::ld(scales + ((kb * QK) / group) * N + n)));
+        }
+    }
+    uint8_t *tile = prepacked + (size_t)tile_id * TILE_BYTES;
+    *reinterpret_cast<uint4 *>(tile + p * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+    if (c == 0)
+        *reinterpret_cast<uint2 *>(tile + TILE_QS_BYTES + g * 8) =
+            make_uint2((uint32_t)ds[0] | ((uint32_t)ds[1] << 16), (uint32_t)ds[2] | ((uint32_t)ds[3] << 16));
+}
+
+// corr[g, n] = 8 * fp16(scale) - zero * scale
+template <typename TS>
+__global__ void __launch_bounds__(128)
+int4g_corr_kernel(const TS *__restrict__ scales, const TS *__restrict__ zeros, int64_t count, float *__restrict__ corr) {
+    const int64_t i = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    if (i >= count) return;
+    const float s = Num<TS>::ld(scales + i), z = Num<TS>::ld(zeros + i);
+    const float d = __half2float(__float2half_rn(s));
+    corr[i] = __fsub_rn(__fmul_rn(8.0f, d), __fmul_rn(z, s));
+}
+
+// addend[m, n] = sum_g corr[g, n] * (sum of x[m, k] over group g).  CTA = one row x 256 columns;
+// the group sums of the row are first built in shared memory.
+template <typename TX>
+__global__ void __launch_bounds__(256)
+int4g_addend_kernel(const TX *__restrict__ x, int64_t ldx, const float *__restrict__ corr, int64_t K, int64_t N,
+                    int64_t group, int G, float *__restrict__ addend) {
+    extern __shared__ float xs[];
+    const int64_t m = blockIdx.y;
+    const TX *xr = x + m * ldx;
+    for (int g = threadIdx.x; g < G; g += 256) {
+        const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
+        float s = 0.0f;
+        for (int64_t k = k0; k < k1; ++k) s += Num<TX>::ld(xr + k);
+        xs[g] = s;
+    }
+    __syncthreads();
+    const int64_t n = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (n >= N) return;
+    float acc = 0.0f;
+    for (int g = 0; g < G; ++g) acc = fmaf(corr[(int64_t)g * N + n], xs[g], acc);
+    addend[m * N + n] = acc;
+}
+
+}  // namespace q4b
+
+using namespace q4b;
+
+static int check_g(int64_t K, int64_t N, int64_t group) {
+    if (K <= 0 || N <= 0 || group <= 0) return Q4B_ERR_ARG;
+    if ((K % 2) || (group % 2)) return Q4B_ERR_SHAPE;
+    if (ceil_div(K, group) > 65535 || K / 2 > 2147483647LL) return Q4B_ERR_SHAPE;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_int4g_quantize(const void *w, int w_dtype, int64_t K, int64_t N, int64_t group, void *packed_out,
+                                  void *scales_out, void *zeros_out, void *stream) {
+    if (w == nullptr || packed_out == nullptr || scales_out == nullptr || zeros_out == nullptr) return Q4B_ERR_ARG;
+    if (int rc = check_g(K, N, group)) return rc;
+    dim3 grid((unsigned)ceil_div(N, 128), (unsigned)ceil_div(K, group));
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t *p = (uint8_t *)packed_out;
+    switch (w_dtype) {
+        case Q4B_F32: int4g_quantize_kernel<float><<<grid, 128, 0, st>>>((const float *)w, K, N, group, p, (float *)scales_out, (float *)zeros_out); break;
+        case Q4B_F16: int4g_quantize_kernel<__half><<<grid, 128, 0, st>>>((const __half *)w, K, N, group, p, (__half *)scales_out, (__half *)zeros_out); break;
+        case Q4B_BF16: int4g_quantize_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16 *)w, K, N, group, p, (__nv_bfloat16 *)scales_out, (__nv_bfloat16 *)zeros_out); break;
+        default: return Q4B_ERR_DTYPE;
+    }
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+template <typename TS>
+static int launch_deq(const void *packed, const void *scales, const void *zeros, int64_t K, int64_t N, int64_t group,
+                      void *w_out, int out_dtype, cudaStream_t st) {
+    dim3 grid((unsigned)ceil_div(N, 128), (unsigned)(K / 2));
+    const uint8_t *p = (const uint8_t *)packed;
+    const TS *s = (const TS *)scales, *z = (const TS *)zeros;
+    switch (out_dtype) {
+        case Q4B_F32: int4g_dequantize_kernel<TS, float><<<grid, 128, 0, st>>>(p, s, z, K, N, group, (float *)w_out); break;
+        case Q4B_F16: int4g_dequantize_kernel<TS, __half><<<grid, 128, 0, st>>>(p, s, z, K, N, group, (__half *)w_out); break;
+        case Q4B_BF16: int4g_dequantize_kernel<TS, __nv_bfloat16><<<grid, 128, 0, st>>>(p, s, z, K, N, group, (__nv_bfloat16 *)w_out); break;
+        default: return Q4B_ERR_DTYPE;
+    }
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_int4g_dequantize(const void *packed, const void *scales, const void *zeros, int sz_dtype, int64_t K,
+                                    int64_t N, int64_t group, void *w_out, int out_dtype, void *stream) {
+    if (packed == nullptr || scales == nullptr || zeros == nullptr || w_out == nullptr) return Q4B_ERR_ARG;
+    if (int rc = check_g(K, N, group)) return rc;
+    if (K / 2 > 65535) return Q4B_ERR_SHAPE;                 // grid.y
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (sz_dtype) {
+        case Q4B_F32: return launch_deq<float>(packed, scales, zeros, K, N, group, w_out, out_dtype, st);
+        case Q4B_F16: return launch_deq<__half>(packed, scales, zeros, K, N, group, w_out, out_dtype, st);
+        case Q4B_BF16: return launch_deq<__nv_bfloat16>(packed, scales, zeros, K, N, group, w_out, out_dtype, st);
+        default: return Q4B_ERR_DTYPE;
+    }
+}
+
+template <typename TS>
+static int launch_prepack(const void *packed, const void *scales, const void *zeros, int64_t K, int64_t N, int64_t group,
+                          void *prepacked_out, float *corr_out, cudaStream_t st) {
+    const int64_t tiles = tiles_k(K) * tiles_n(N);
+    int4g_prepack_kernel<TS><<<(unsigned)ceil_div(tiles, 4), 128, 0, st>>>((const uint8_t *)packed, (const TS *)scales, K, N,
+                                                                           group, (uint8_t *)prepacked_out);
+    Q4B_LAUNCH_CHECK();
+    const int64_t count = ceil_div(K, group) * N;
+    int4g_corr_kernel<TS><<<(unsigned)ceil_div(count, 128), 128, 0, st>>>((const TS *)scales, (const TS *)zeros, count, corr_out);
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_int4g_prepack(const void *packed, const void *scales, const void *zeros, int sz_dtype, int64_t K,
+                                 int64_t N, int64_t group, void *prepacked_out, float *corr_out, void *stream) {
+    if (packed == nullptr || scales == nullptr || zeros == nullptr || prepacked_out == nullptr || corr_out == nullptr)
+        return Q4B_ERR_ARG;
+    if (int rc = check_g(K, N, group)) return rc;
+    if ((K % QK) || (group % QK)) return Q4B_ERR_SHAPE;       // a 32-k block must lie inside one group
+    if (!aligned(prepacked_out, 16)) return Q4B_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (sz_dtype) {
+        case Q4B_F32: return launch_prepack<float>(packed, scales, zeros, K, N, group, prepacked_out, corr_out, st);
+        case Q4B_F16: return launch_prepack<__half>(packed, scales, zeros, K, N, group, prepacked_out, corr_out, st);
+        case Q4B_BF16: return launch_prepack<__nv_bfloat16>(packed, scales, zeros, K, N, group, prepacked_out, corr_out, st);
+        default: return Q4B_ERR_DTYPE;
+    }
+}
+
+extern "C" int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr, int64_t K,
+                                int64_t N, int64_t group, float *addend_out, void *stream) {
+    if (x == nullptr || corr == nullptr || addend_out == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || ldx < K) return Q4B_ERR_ARG;
+    if (int rc = check_g(K, N, group)) return rc;
+    const int64_t G = ceil_div(K, group);
+    if (G > 8192 || M > 65535) return Q4B_ERR_TOO_LARGE;
+    dim3 grid((unsigned)ceil_div(N, 256), (unsigned)M);
+    const size_t smem = (size_t)G * sizeof(float);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case Q4B_F16: int4g_addend_kernel<__half><<<grid, 256, smem, st>>>((const __half *)x, ldx, corr, K, N, group, (int)G, addend_out); break;
+        case Q4B_BF16: int4g_addend_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>((const __nv_bfloat16 *)x, ldx, corr, K, N, group, (int)G, addend_out); break;
+        default: return Q4B_ERR_DTYPE;
+    }
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}

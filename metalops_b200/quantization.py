@@ -148,7 +148,8 @@ def dequantize_ggml_q4_0(blocks: torch.Tensor, dtype: Optional[torch.dtype] = No
 
 
 def _matmul_prepacked(X: torch.Tensor, pre: Q4Prepacked, out: Optional[torch.Tensor] = None,
-                      flags: int = _cabi.FLAG_NONE, kernel: str = "auto") -> torch.Tensor:
+                      flags: int = _cabi.FLAG_NONE, kernel: str = "auto",
+                      addend: Optional[torch.Tensor] = None) -> torch.Tensor:
     _cabi.require_device(X, "X")
     if X.device != pre.device:
         raise RuntimeError(f"X is on {X.device} but the weights are on {pre.device}")
@@ -168,9 +169,13 @@ def _matmul_prepacked(X: torch.Tensor, pre: Q4Prepacked, out: Optional[torch.Ten
     if y.shape != (M, pre.N) or y.dtype != x.dtype or y.stride(1) != 1:
         raise RuntimeError("out must be [M, N], X's dtype, unit inner stride")
     lib = _cabi.load()
-    fn = {"auto": lib.q4b_matmul, "gemv": lib.q4b_gemv, "gemm": lib.q4b_gemm}[kernel]
+    fn = {"auto": lib.q4b_matmul_addend, "gemv": lib.q4b_gemv_addend, "gemm": lib.q4b_gemm_addend}[kernel]
+    if addend is not None and (addend.dtype != torch.float32 or tuple(addend.shape) != (M, pre.N)
+                               or addend.stride(1) != 1 or addend.device != x.device):
+        raise RuntimeError("addend must be a float32 [M, N] tensor on X's device with unit inner stride")
     with torch.cuda.device(x.device):
         rc = fn(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.data.data_ptr(), pre.K, pre.N,
+                addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
                 y.data_ptr(), y.stride(0), flags, _cabi.stream_ptr(x.device))
     _cabi.check(rc, "matmul_ggml_q4_0")
     return y.float() if in_dtype == torch.float32 else y
@@ -204,95 +209,196 @@ def matmul_ggml_q4_0(X: torch.Tensor, W_blocks) -> torch.Tensor:
     return _matmul_prepacked(X, pre)
 
 
-# ---------------------------------------------------------------------------------------
-# Group-wise asymmetric INT4 / INT8 entry points of the reference (quantization.py:26-286).
-# Their native kernels are not part of this build yet; they raise rather than fall back.
-# ---------------------------------------------------------------------------------------
 
-def _not_built(name: str):
-    raise NotImplementedError(
-        f"{name}: the group-wise INT4/INT8 format has no sm_100a kernel in this build yet, and "
-        "there is no CPU fallback by design; use the q4_0 entry points")
 
+# ---------------------------------------------------------------------------------------
+# Group-wise asymmetric INT4 (quantization.py:26-239 of the reference): weight_packed [K/2, N],
+# scales / zeros [ceil(K/group), N], W = (q - zero) * scale.
+# ---------------------------------------------------------------------------------------
 
 def quantize_int4(weight: torch.Tensor, group_size: int = 128) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    _not_built("quantize_int4")
+    """Quantize ``weight [K, N]`` to INT4 with per-group scale and zero point; returns
+    ``(weight_packed uint8 [K/2, N], scales [groups, N], zeros [groups, N])``, scales and zeros in
+    the weight's dtype.  Bit-identical to the reference's Python loop (quantization.py:26-93)."""
+    if weight.dim() != 2:
+        raise ValueError("weight must be 2-D [K, N]")
+    _cabi.require_device(weight, "weight")
+    if weight.dtype not in _cabi.DTYPE_CODE:
+        raise RuntimeError(f"unsupported weight dtype {weight.dtype}")
+    w = weight.contiguous()
+    K, N = w.shape
+    if K % 2 or group_size % 2 or group_size <= 0:
+        raise RuntimeError("quantize_int4 needs an even K and an even, positive group_size")
+    ng = (K + group_size - 1) // group_size
+    packed = torch.empty((K // 2, N), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((ng, N), dtype=w.dtype, device=w.device)
+    zeros = torch.empty((ng, N), dtype=w.dtype, device=w.device)
+    with torch.cuda.device(w.device):
+        rc = _cabi.load().q4b_int4g_quantize(w.data_ptr(), _cabi.DTYPE_CODE[w.dtype], K, N, group_size,
+                                             packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                             _cabi.stream_ptr(w.device))
+    _cabi.check(rc, "quantize_int4")
+    return packed, scales, zeros
 
 
-def dequantize_int4(W_packed, scales, zeros, group_size: int = 128, dtype: Optional[torch.dtype] = None):
-    _not_built("dequantize_int4")
+def _check_int4g(W_packed, scales, zeros, group_size):
+    _cabi.require_device(W_packed, "W_packed")
+    if W_packed.dtype != torch.uint8 or W_packed.dim() != 2:
+        raise RuntimeError("W_packed must be uint8 [K/2, N]")
+    K, N = W_packed.shape[0] * 2, W_packed.shape[1]
+    ng = (K + group_size - 1) // group_size
+    if tuple(scales.shape) != (ng, N) or tuple(zeros.shape) != (ng, N) or scales.dtype != zeros.dtype:
+        raise RuntimeError(f"scales and zeros must both be [{ng}, {N}] of one dtype")
+    if scales.dtype not in _cabi.DTYPE_CODE:
+        raise RuntimeError(f"unsupported scales dtype {scales.dtype}")
+    if scales.device != W_packed.device or zeros.device != W_packed.device:
+        raise RuntimeError("W_packed, scales and zeros must be on the same device")
+    return K, N
 
 
-def matmul_int4(X, W_packed, scales, zeros, group_size: int = 128):
-    _not_built("matmul_int4")
+def dequantize_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int = 128,
+                    dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``W[k] = ((q - zero) * scale)`` in fp32, cast to ``dtype`` (default fp16) — quantization.py:96-153."""
+    if dtype is None:
+        dtype = torch.float16
+    K, N = _check_int4g(W_packed, scales, zeros, group_size)
+    if dtype not in _cabi.DTYPE_CODE:
+        raise RuntimeError(f"unsupported output dtype {dtype}")
+    p, s, z = W_packed.contiguous(), scales.contiguous(), zeros.contiguous()
+    W = torch.empty((K, N), dtype=dtype, device=p.device)
+    with torch.cuda.device(p.device):
+        rc = _cabi.load().q4b_int4g_dequantize(p.data_ptr(), s.data_ptr(), z.data_ptr(), _cabi.DTYPE_CODE[s.dtype], K, N,
+                                               group_size, W.data_ptr(), _cabi.DTYPE_CODE[dtype], _cabi.stream_ptr(p.device))
+    _cabi.check(rc, "dequantize_int4")
+    return W
+
+
+class Int4GPrepacked:
+    """A group-wise INT4 weight converted for the matmul kernels: streaming tiles (block scale =
+    fp16 of the group scale) plus the fp32 per-group constant ``8*d - zero*scale``."""
+
+    __slots__ = ("tiles", "corr", "group_size")
+
+    def __init__(self, tiles: Q4Prepacked, corr: torch.Tensor, group_size: int):
+        self.tiles, self.corr, self.group_size = tiles, corr, group_size
+
+
+def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int = 128) -> Int4GPrepacked:
+    """One-time conversion of a group-wise INT4 weight (cached on ``W_packed``).  Needs
+    ``K % 32 == 0`` and ``group_size % 32 == 0``, and scales inside fp16's range."""
+    key = (W_packed._version, scales.data_ptr(), scales._version, zeros.data_ptr(), zeros._version, group_size)
+    cached = getattr(W_packed, "_q4b_int4g", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    K, N = _check_int4g(W_packed, scales, zeros, group_size)
+    if K % QK4_0 or group_size % QK4_0:
+        raise RuntimeError("the fused INT4 matmul needs K and group_size to be multiples of 32")
+    p, s, z = W_packed.contiguous(), scales.contiguous(), zeros.contiguous()
+    tiles = _alloc_prepacked(K, N, p.device)
+    corr = torch.empty(s.shape, dtype=torch.float32, device=p.device)
+    with torch.cuda.device(p.device):
+        rc = _cabi.load().q4b_int4g_prepack(p.data_ptr(), s.data_ptr(), z.data_ptr(), _cabi.DTYPE_CODE[s.dtype], K, N,
+                                            group_size, tiles.data_ptr(), corr.data_ptr(), _cabi.stream_ptr(p.device))
+    _cabi.check(rc, "prepack_int4")
+    out = Int4GPrepacked(Q4Prepacked(tiles, K, N), corr, group_size)
+    try:
+        W_packed._q4b_int4g = (key, out)
+    except AttributeError:
+        pass
+    return out
+
+
+def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    in_dtype = X2.dtype
+    x = X2.half() if in_dtype == torch.float32 else X2
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"X must be float16, bfloat16 or float32 (got {in_dtype})")
+    x = x.contiguous()
+    M, K, N = x.shape[0], pre.tiles.K, pre.tiles.N
+    assert x.shape[1] == K, f"X K dim ({x.shape[1]}) must match weight K ({K})"
+    if M == 0:
+        return torch.empty((0, N), dtype=in_dtype, device=x.device)
+    addend = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _cabi.load().q4b_int4g_addend(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.corr.data_ptr(),
+                                           K, N, pre.group_size, addend.data_ptr(), _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "matmul_int4")
+    if bias is not None:
+        addend += bias.float()
+    y = _matmul_prepacked(x, pre.tiles, addend=addend)
+    return y.float() if in_dtype == torch.float32 else y
+
+
+def matmul_int4(X: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
+                group_size: int = 128) -> torch.Tensor:
+    """``Y = X @ ((q - zero) * scale)`` for ``X [M, K]`` or ``[B, M, K]`` — quantization.py:156-239.
+
+    Runs the fused kernels (decode GEMV for M <= 16, tcgen05 GEMM above) on a one-time
+    conversion of the weight; the zero-point term enters as an fp32 addend before the single
+    rounding.  Output dtype = ``X.dtype``."""
+    _cabi.require_device(X, "X")
+    batched = X.dim() == 3
+    X2 = X.reshape(-1, X.shape[-1]) if batched else X
+    if X2.dim() != 2:
+        raise RuntimeError("X must be [M, K] or [B, M, K]")
+    Y = _matmul_int4_prepacked(X2, prepack_int4(W_packed, scales, zeros, group_size))
+    return Y.view(X.shape[0], X.shape[1], -1) if batched else Y
 
 
 def matmul_int8(X, W_packed, scales, zeros, group_size: int = 128):
-    _not_built("matmul_int8")
+    """INT8 group-wise matmul of the reference (quantization.py:242-286): not part of the INT4
+    path; no sm_100a kernel is built for it and there is no CPU fallback."""
+    raise NotImplementedError("matmul_int8 has no sm_100a kernel in this build (and no fallback by design)")
 
 
 class Int4Linear(nn.Module):
-    """INT4 linear layer with the constructor, methods and ``extra_repr`` of the reference's
-    ``Int4Linear`` (quantization.py:457-612), storing the weight as q4_0 blocks.
+    """INT4 quantized linear layer with the reference's constructor, buffers, methods and
+    ``extra_repr`` (quantization.py:457-612): ``weight_packed [in/2, out]``, ``scales`` /
+    ``zeros [groups, out]`` and ``bias`` are the serialised state, so checkpoints interchange.
 
-    Buffers: ``weight_blocks`` uint8 ``[in/32, out, 18]`` (serialised) and ``bias``.  The
-    streaming copy used by the kernels is derived state, rebuilt after ``load_state_dict`` /
-    ``.to()``.  ``group_size`` is accepted for signature compatibility; q4_0 fixes it at 32.
-    ``dequant_on_load=True`` keeps a dense fp16 copy and uses a plain fp16 matmul exactly like
-    the reference's "hybrid" mode (quantization.py:593-597); the default here is ``False``
-    because the fused kernels are the point of this build.
-    """
+    ``dequant_on_load=True`` (the reference's default) keeps a dense fp16 copy and multiplies with
+    it, like the reference's "hybrid" mode; ``keep_quantized()`` or ``dequant_on_load=False`` runs
+    the fused kernels on the packed weight (the reference's ``int4_kernel`` mode), bias included
+    as an fp32 term before the output rounding."""
 
     def __init__(self, in_features: int, out_features: int, group_size: int = 128, bias: bool = True,
                  device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None,
-                 dequant_on_load: bool = False):
+                 dequant_on_load: bool = True):
         super().__init__()
-        if in_features % QK4_0:
-            raise AssertionError(f"in_features ({in_features}) must be divisible by {QK4_0}")
         self.in_features = in_features
         self.out_features = out_features
         self.group_size = group_size
         self._dequant_on_load = dequant_on_load
-        blocks = torch.zeros((in_features // QK4_0, out_features, BLOCK_Q4_0_SIZE), dtype=torch.uint8, device=device)
-        blocks[:, :, 1] = 0x3C
-        blocks[:, :, 2:] = 0x88       # all-zero weight: d = 1.0, q = 8
-        self.register_buffer("weight_blocks", blocks)
+        self.register_buffer("weight_packed", torch.zeros((in_features // 2, out_features), dtype=torch.uint8, device=device))
+        num_groups = (in_features + group_size - 1) // group_size
+        self.register_buffer("scales", torch.ones((num_groups, out_features), dtype=dtype or torch.float32, device=device))
+        self.register_buffer("zeros", torch.zeros((num_groups, out_features), dtype=dtype or torch.float32, device=device))
         self._weight_dequant: Optional[torch.Tensor] = None
-        self._prepacked: Optional[Q4Prepacked] = None
-        self._prepacked_key = None
         if bias:
             self.register_buffer("bias", torch.zeros(out_features, dtype=dtype or torch.float32, device=device))
         else:
             self.register_parameter("bias", None)
 
-    def _weights(self) -> Q4Prepacked:
-        wb = self.weight_blocks
-        key = (wb.data_ptr(), wb._version, wb.device)
-        if self._prepacked is None or self._prepacked_key != key:
-            self._prepacked = prepack_ggml_q4_0(wb)
-            self._prepacked_key = key
-        return self._prepacked
-
     def dequantize(self, dtype: Optional[torch.dtype] = None) -> None:
-        """Keep a dense copy (default fp16) and use a plain matmul (quantization.py:519-534)."""
-        self._weight_dequant = dequantize_ggml_q4_0(self.weight_blocks, dtype or torch.float16)
+        """Keep a dense copy (default fp16) for a plain matmul; not serialised (quantization.py:519-534)."""
+        self._weight_dequant = dequantize_int4(self.weight_packed, self.scales, self.zeros, self.group_size,
+                                               dtype or torch.float16)
         self._dequant_on_load = True
 
     def keep_quantized(self) -> None:
-        """Drop the dense copy; forward uses the fused q4_0 kernels (quantization.py:536-544)."""
+        """Drop the dense copy and use the fused INT4 kernels (quantization.py:536-544)."""
         self._weight_dequant = None
         self._dequant_on_load = False
 
     @classmethod
-    def from_float(cls, module: nn.Linear, group_size: int = 128, dequant_on_load: bool = False) -> "Int4Linear":
-        """Quantize an ``nn.Linear`` (quantization.py:546-589).  The ``[out, in]`` weight is read
-        in place as the transposed ``[in, out]`` matrix; no transposed copy is made."""
+    def from_float(cls, module: nn.Linear, group_size: int = 128, dequant_on_load: bool = True) -> "Int4Linear":
+        """Quantize an ``nn.Linear`` (quantization.py:546-589)."""
         q = cls(module.in_features, module.out_features, group_size=group_size, bias=module.bias is not None,
                 device=module.weight.device, dtype=module.weight.dtype, dequant_on_load=dequant_on_load)
-        blocks, pre = _quantize_impl(module.weight.data.t(), True, True)
-        q.weight_blocks = blocks
-        q._prepacked = pre
-        q._prepacked_key = (blocks.data_ptr(), blocks._version, blocks.device)
+        packed, scales, zeros = quantize_int4(module.weight.data.T.contiguous(), group_size)
+        q.weight_packed.copy_(packed)
+        q.scales.copy_(scales)
+        q.zeros.copy_(zeros)
         if module.bias is not None:
             q.bias.copy_(module.bias.data)
         if dequant_on_load:
@@ -300,17 +406,61 @@ class Int4Linear(nn.Module):
         return q
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        lead = x.shape[:-1]
-        x2 = x.reshape(-1, x.shape[-1])
         if self._weight_dequant is not None:
-            y = (x2.to(self._weight_dequant.dtype) @ self._weight_dequant).to(x.dtype)
-        else:
-            y = _matmul_prepacked(x2, self._weights())
-        if self.bias is not None:
-            y = y + self.bias
+            x_half = x.half() if x.dtype != torch.float16 else x
+            y = (x_half @ self._weight_dequant).to(x.dtype)
+            return y + self.bias if self.bias is not None else y
+        lead = x.shape[:-1]
+        pre = prepack_int4(self.weight_packed, self.scales, self.zeros, self.group_size)
+        y = _matmul_int4_prepacked(x.reshape(-1, x.shape[-1]), pre, bias=self.bias)
+        if self.bias is not None and self.bias.dtype != y.dtype:
+            y = y.to(torch.promote_types(y.dtype, self.bias.dtype))     # the reference's `y + bias` promotes
         return y.reshape(*lead, self.out_features)
 
     def extra_repr(self) -> str:
         mode = "fast_fp16" if self._weight_dequant is not None else "int4_kernel"
         return (f"in_features={self.in_features}, out_features={self.out_features}, "
                 f"group_size={self.group_size}, bias={self.bias is not None}, mode={mode}")
+
+
+class Q4Linear(nn.Module):
+    """Linear layer stored as GGML block_q4_0 (``weight_blocks`` uint8 ``[in/32, out, 18]`` + ``bias``),
+    always computed by the fused q4_0 kernels.  Not in the reference (its ``Int4Linear`` uses the
+    group-wise format above); this is the module form of ``matmul_ggml_q4_0``."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True,
+                 device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None):
+        super().__init__()
+        if in_features % QK4_0:
+            raise AssertionError(f"in_features ({in_features}) must be divisible by {QK4_0}")
+        self.in_features, self.out_features = in_features, out_features
+        blocks = torch.zeros((in_features // QK4_0, out_features, BLOCK_Q4_0_SIZE), dtype=torch.uint8, device=device)
+        blocks[:, :, 1] = 0x3C
+        blocks[:, :, 2:] = 0x88       # all-zero weight: d = 1.0, q = 8
+        self.register_buffer("weight_blocks", blocks)
+        if bias:
+            self.register_buffer("bias", torch.zeros(out_features, dtype=dtype or torch.float32, device=device))
+        else:
+            self.register_parameter("bias", None)
+
+    @classmethod
+    def from_float(cls, module: nn.Linear) -> "Q4Linear":
+        """The ``[out, in]`` weight is read in place as the transposed ``[in, out]`` matrix."""
+        q = cls(module.in_features, module.out_features, bias=module.bias is not None,
+                device=module.weight.device, dtype=module.weight.dtype)
+        q.weight_blocks = quantize_ggml_q4_0(module.weight.data.t())
+        if module.bias is not None:
+            q.bias.copy_(module.bias.data)
+        return q
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        addend = None
+        if self.bias is not None and x2.shape[0] > 0:
+            addend = self.bias.float().unsqueeze(0).expand(x2.shape[0], -1).contiguous()
+        y = _matmul_prepacked(x2, prepack_ggml_q4_0(self.weight_blocks), addend=addend)
+        return y.reshape(*lead, self.out_features)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, format=q4_0"

@@ -1,0 +1,132 @@
+"""GPU parity of the group-wise asymmetric INT4 path (quantize_int4, dequantize_int4,
+matmul_int4, Int4Linear) against fixtures produced by the reference module and the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_tensor, load_golden
+from oracle import q4_0_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = 5e-3
+
+CASES = [("g128_f32", 128), ("g64_f32", 64), ("g128_f16", 128), ("g128_ragged", 128)]
+
+
+@pytest.fixture(scope="module")
+def mo(cuda_dev):
+    import metalops_b200
+    assert metalops_b200.has_native_kernels()
+    return metalops_b200
+
+
+def same_bits(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Equal including NaNs in the same places (a constant fp16 group yields NaN in the reference)."""
+    a, b = a.cpu(), b.cpu()
+    return a.dtype == b.dtype and a.shape == b.shape and bool(torch.allclose(a.float(), b.float(), rtol=0, atol=0, equal_nan=True))
+
+
+@pytest.mark.parametrize("name,gs", CASES)
+def test_golden_quantize_dequantize(mo, cuda_dev, name, gs):
+    z = load_golden("int4_groupwise.npz")
+    w = golden_tensor(z, f"{name}.w")
+    packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), gs)
+    assert scales.dtype == w.dtype and zeros.dtype == w.dtype and packed.dtype == torch.uint8
+    assert same_bits(scales, golden_tensor(z, f"{name}.scales"))
+    assert same_bits(zeros, golden_tensor(z, f"{name}.zeros"))
+    gp = golden_tensor(z, f"{name}.packed")
+    finite_cols = torch.isfinite(golden_tensor(z, f"{name}.zeros").float()).all(dim=0)
+    # columns whose zero point is not finite go through an undefined NaN -> uint8 cast in the reference
+    assert torch.equal(packed.cpu()[:, finite_cols], gp[:, finite_cols])
+    deq = mo.dequantize_int4(gp.to(cuda_dev), golden_tensor(z, f"{name}.scales").to(cuda_dev),
+                             golden_tensor(z, f"{name}.zeros").to(cuda_dev), gs, torch.float32)
+    assert same_bits(deq, golden_tensor(z, f"{name}.deq_f32"))
+    assert mo.dequantize_int4(packed, scales, zeros, gs).dtype == torch.float16
+
+
+@pytest.mark.parametrize("name,gs", CASES)
+def test_golden_matmul_int4(mo, cuda_dev, name, gs):
+    z = load_golden("int4_groupwise.npz")
+    x = golden_tensor(z, f"{name}.x")
+    packed = golden_tensor(z, f"{name}.packed").to(cuda_dev)
+    scales = golden_tensor(z, f"{name}.scales").to(cuda_dev)
+    zeros = golden_tensor(z, f"{name}.zeros").to(cuda_dev)
+    y = mo.matmul_int4(x.to(cuda_dev), packed, scales, zeros, gs)
+    ref = golden_tensor(z, f"{name}.y")
+    assert y.dtype == x.dtype and tuple(y.shape) == tuple(ref.shape)
+    cols = torch.isfinite(ref.float()).all(dim=0)
+    assert cols.sum() >= ref.shape[1] - 1
+    assert orc.rel_l2(y.cpu()[:, cols], ref[:, cols]) <= TOL
+    ref32 = x.float() @ golden_tensor(z, f"{name}.deq_f32")
+    assert orc.rel_l2(y.cpu()[:, cols], ref32[:, cols]) <= TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_seeded_quantize_vs_oracle(mo, cuda_dev, dtype):
+    g = torch.Generator().manual_seed(21)
+    w = (torch.randn(1024, 300, generator=g) * 0.05).to(dtype)
+    packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), 128)
+    op, os_, oz = orc.quantize_int4_groupwise(w, 128)
+    assert torch.equal(packed.cpu(), op)
+    assert same_bits(scales, os_) and same_bits(zeros, oz)
+    assert same_bits(mo.dequantize_int4(packed, scales, zeros, 128, torch.float32),
+                     orc.dequantize_int4_groupwise(op, os_, oz, 128, torch.float32))
+
+
+@pytest.mark.parametrize("M,xdtype", [(1, torch.float16), (8, torch.float16), (16, torch.bfloat16), (70, torch.bfloat16),
+                                      (200, torch.float16)])
+def test_seeded_matmul_int4(mo, cuda_dev, M, xdtype):
+    g = torch.Generator().manual_seed(50 + M)
+    K, N = 2048, 1040
+    w = torch.randn(K, N, generator=g) * 0.03 + 0.01            # non-zero mean: the zero-point term matters
+    x = torch.randn(M, K, generator=g).to(xdtype)
+    packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), 128)
+    y = mo.matmul_int4(x.to(cuda_dev), packed, scales, zeros, 128)
+    ref = x.float() @ orc.dequantize_int4_groupwise(packed.cpu(), scales.cpu(), zeros.cpu(), 128, torch.float32)
+    err = orc.rel_l2(y, ref)
+    assert err <= (1e-3 if xdtype == torch.float16 else TOL), f"rel-L2 {err:.3e}"
+    # batched input [B, M, K] like the reference accepts
+    yb = mo.matmul_int4(x.to(cuda_dev).unsqueeze(0).repeat(2, 1, 1), packed, scales, zeros, 128)
+    assert tuple(yb.shape) == (2, M, N)
+    assert orc.rel_l2(yb[1], ref) <= TOL and orc.rel_l2(yb[0], ref) <= TOL     # 2M rows may take another kernel
+    assert mo.quantization.wait_status(cuda_dev) == 0
+
+
+def test_int4_linear_matches_reference_module(mo, cuda_dev):
+    z = load_golden("int4_linear.npz")
+    lin = torch.nn.Linear(256, 24, bias=True)
+    lin.weight.data.copy_(golden_tensor(z, "lin.weight"))
+    lin.bias.data.copy_(golden_tensor(z, "lin.bias"))
+    lin = lin.to(cuda_dev)
+    ql = mo.Int4Linear.from_float(lin, group_size=128, dequant_on_load=False)
+    sd = ql.state_dict()
+    assert sorted(sd.keys()) == sorted(z["state_keys"].tolist())
+    for k in sd:
+        assert same_bits(sd[k], golden_tensor(z, f"sd.{k}")), k
+    assert ql.extra_repr() == str(z["repr_int4"])
+    x = golden_tensor(z, "x").to(cuda_dev)
+    y = ql(x)
+    assert y.dtype == torch.float32
+    assert orc.rel_l2(y, golden_tensor(z, "y_int4")) <= TOL
+    ql.dequantize()
+    assert ql.extra_repr() == str(z["repr_fast"])
+    assert orc.rel_l2(ql(x), golden_tensor(z, "y_fp16cache")) <= TOL
+    ql.keep_quantized()
+    assert torch.equal(ql(x), y)
+    # a checkpoint written by the reference loads into a fresh module
+    fresh = mo.Int4Linear(256, 24, group_size=128, dequant_on_load=False, device=cuda_dev)
+    fresh.load_state_dict({k: golden_tensor(z, f"sd.{k}") for k in sd})
+    assert torch.equal(fresh(x), y)
+
+
+def test_int4_errors(mo, cuda_dev):
+    w = torch.zeros(64, 8, device=cuda_dev)
+    with pytest.raises(RuntimeError):
+        mo.quantize_int4(torch.zeros(64, 8), 32)                       # CPU tensor: no fallback
+    with pytest.raises(RuntimeError):
+        mo.quantize_int4(w, 31)                                        # odd group
+    p, s, zz = mo.quantize_int4(w + 1.0, 16)
+    with pytest.raises(RuntimeError):
+        mo.matmul_int4(torch.zeros(1, 64, device=cuda_dev, dtype=torch.float16), p, s, zz, 16)   # group % 32 != 0
+    with pytest.raises(NotImplementedError):
+        mo.matmul_int8(None, None, None, None)
