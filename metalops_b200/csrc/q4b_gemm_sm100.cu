@@ -31,12 +31,12 @@ namespace q4b {
 namespace gemm {
 
 constexpr int BM = 256, BN = 256, BK = 64, HALF_M = 128;
-constexpr int SA = 3, SW = 4, SB = 2;                // ring depths
+constexpr int SA = 3, SB = 2;                        // ring depths of the X and B operand stages
+constexpr int SW_MAX = 16;                           // packed-weight ring: depth chosen per launch, see w_ring_depth
 constexpr int A_BYTES = BM * BK * 2;                 // 32768
 constexpr int A_HALF_BYTES = HALF_M * BK * 2;        // 16384
 constexpr int B_BYTES = BN * BK * 2;                 // 32768
 constexpr int W_TILES = BN / TILE_N;                 // 16 prepacked tiles per step
-constexpr int W_BYTES = W_TILES * TILE_BYTES;        // 9216
 #ifndef Q4B_GEMM_DEQ_WARPS
 #define Q4B_GEMM_DEQ_WARPS 8
 #endif
@@ -50,11 +50,18 @@ constexpr int THREADS = (FIRST_EPI2_WARP + 4) * 32;              // 608
 constexpr int TMEM_COLS = 512;                       // one 256-column fp32 accumulator per half
 constexpr int SMEM_A = 0;
 constexpr int SMEM_B = SMEM_A + SA * A_BYTES;
-constexpr int SMEM_W = SMEM_B + SB * B_BYTES;
-constexpr int SMEM_BAR = SMEM_W + SW * W_BYTES;
-constexpr int NUM_BARS = 2 * (SA + SW + SB) + 2;
-constexpr int SMEM_USED = SMEM_BAR + NUM_BARS * 8 + 16;
-constexpr int SMEM_DYN = SMEM_USED + 1024;           // slack to align the base to 1024 bytes
+constexpr int SMEM_BAR = SMEM_B + SB * B_BYTES;
+constexpr int NUM_BARS = 2 * (SA + SW_MAX + SB) + 2;
+constexpr int SMEM_W = SMEM_BAR + ((NUM_BARS * 8 + 127) / 128) * 128;
+constexpr int SMEM_DYN = 227 * 1024 - 256;           // all a CTA may have, less the few static words
+constexpr int SMEM_W_BYTES = SMEM_DYN - 1024 - SMEM_W;   // 1024: slack to align the base
+// Packed weights arrive about a microsecond after they are asked for, whatever the step length, so
+// the ring holds as many steps as shared memory allows: 7 at 256 columns per tile, 14 at 128.  A
+// short step (few rows of X) then still has enough bytes in flight to keep HBM busy.
+__host__ __device__ inline int w_ring_depth(int bn) {
+    const int d = SMEM_W_BYTES / ((bn / TILE_N) * TILE_BYTES);
+    return d < SW_MAX ? d : SW_MAX;
+}
 constexpr long long WAIT_LIMIT_CYCLES = 1LL << 28;   // ~0.15 s; far above any legitimate wait
 
 __device__ int g_gemm_status = 0;
@@ -216,10 +223,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     auto bar_full_a = [&](int s) { return bar0 + 8u * s; };                          // X tile landed
     auto bar_empty_a = [&](int s) { return bar0 + 8u * (SA + s); };                  // its MMAs retired
     auto bar_full_w = [&](int s) { return bar0 + 8u * (2 * SA + s); };               // packed weights landed
-    auto bar_empty_w = [&](int s) { return bar0 + 8u * (2 * SA + SW + s); };         // dequantisers done reading
-    auto bar_full_b = [&](int s) { return bar0 + 8u * (2 * SA + 2 * SW + s); };      // B operand written
-    auto bar_empty_b = [&](int s) { return bar0 + 8u * (2 * SA + 2 * SW + SB + s); };  // its MMAs retired
-    const uint32_t bar_tfull = bar0 + 8u * (2 * (SA + SW + SB));                     // accumulators complete
+    auto bar_empty_w = [&](int s) { return bar0 + 8u * (2 * SA + SW_MAX + s); };         // dequantisers done reading
+    auto bar_full_b = [&](int s) { return bar0 + 8u * (2 * SA + 2 * SW_MAX + s); };      // B operand written
+    auto bar_empty_b = [&](int s) { return bar0 + 8u * (2 * SA + 2 * SW_MAX + SB + s); };  // its MMAs retired
+    const uint32_t bar_tfull = bar0 + 8u * (2 * (SA + SW_MAX + SB));                     // accumulators complete
     const uint32_t bar_tempty = bar_tfull + 8u;                                      // accumulators drained
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -228,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < SA; ++s) { mbar_init(bar_full_a(s), 1); mbar_init(bar_empty_a(s), 1); }
-        for (int s = 0; s < SW; ++s) { mbar_init(bar_full_w(s), 1); mbar_init(bar_empty_w(s), NUM_DEQ_WARPS); }
+        for (int s = 0; s < SW_MAX; ++s) { mbar_init(bar_full_w(s), 1); mbar_init(bar_empty_w(s), NUM_DEQ_WARPS); }
         for (int s = 0; s < SB; ++s) { mbar_init(bar_full_b(s), NUM_DEQ_WARPS); mbar_init(bar_empty_b(s), 1); }
         mbar_init(bar_tfull, 1);
         mbar_init(bar_tempty, 8);
@@ -246,6 +253,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     const int NT = (int)tiles_n(N);                    // prepacked 16-column tiles
     // bn = columns per tile (multiple of 32, at most BN), chosen by the host to even out the waves
     const int w_tiles = bn / TILE_N;
+    const int sw = w_ring_depth(bn);                   // packed-weight ring: depth and stage size
+    const int w_stage = w_tiles * TILE_BYTES;
     const int num_mt = (M + BM - 1) / BM, num_nt = (N + bn - 1) / bn;
     const int num_tiles = num_mt * num_nt;
     const int k_steps = (K + BK - 1) / BK;
@@ -279,9 +288,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                 if (lane == 0) mbar_arrive_expect_tx(bar_full_w(w.s), (uint32_t)(valid * TILE_BYTES));
                 __syncwarp();
                 if (lane < valid)
-                    bulk_load(base + SMEM_W + w.s * W_BYTES + lane * TILE_BYTES, src + (size_t)ks * TILE_BYTES, TILE_BYTES,
+                    bulk_load(base + SMEM_W + w.s * w_stage + lane * TILE_BYTES, src + (size_t)ks * TILE_BYTES, TILE_BYTES,
                               bar_full_w(w.s));
-                w.advance(SW);
+                w.advance(sw);
             }
         }
     } else if (warp == WARP_MMA) {
@@ -406,7 +415,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
 #pragma unroll
                 for (int i = 0; i < TILES_PER_WARP; ++i) {
                     if (dw + i * NUM_DEQ_WARPS >= valid) break;
-                    const uint32_t wst = base + SMEM_W + w.s * W_BYTES + i * NUM_DEQ_WARPS * TILE_BYTES;
+                    const uint32_t wst = base + SMEM_W + w.s * w_stage + i * NUM_DEQ_WARPS * TILE_BYTES;
                     const uint32_t bst = base + SMEM_B + b.s * B_BYTES + i * NUM_DEQ_WARPS * 2048;
                     uint4 qw;
                     uint2 dq;
@@ -440,7 +449,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
 #ifdef Q4B_GEMM_PROFILE
                 prof[2] += clock64() - _work0;
 #endif
-                w.advance(SW);
+                w.advance(sw);
                 b.advance(SB);
             }
         }
