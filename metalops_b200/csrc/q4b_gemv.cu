@@ -31,6 +31,21 @@ constexpr int GEMV_SPIN_LIMIT = 1 << 22;            // try_wait polls before giv
 
 __device__ int g_wait_status = 0;                  // first bounded wait of this file that gave up
 
+#ifdef Q4B_GEMV_TRACE
+// development aid: one record per CTA (weights pointer, block | sm << 32, four global-timer stamps)
+constexpr int TRACE_MAX = 1 << 16;
+__device__ unsigned long long g_trace[TRACE_MAX * 6];
+__device__ unsigned int g_trace_n = 0;
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE_STAMP(i) if (threadIdx.x == 0) trace_t[i] = trace_now()
+#else
+#define TRACE_STAMP(i)
+#endif
+
 // Shared-memory geometry of one ring slot: CHUNK weight tiles, then the x rows.  The row
 // stride is 64 bytes more than a multiple of 128 so that the eight (row, k-octet) pairs a
 // quarter warp reads fall into eight different 16-byte bank groups.
@@ -48,6 +63,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// On the lanes where `pred` holds: arm `bar` with the bytes of both copies and start them (weights,
+// then the activation slice).  Predicated instead of branched, so the other lanes lose no time.
+__device__ __forceinline__ void refill_pred(bool pred, uint32_t bar, uint32_t dst_w, const void *src_w, uint32_t wb,
+                                            uint32_t dst_x, const void *src_x, uint32_t xb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 t;\n\t"
+        "setp.ne.u32 p, %0, 0;\n\t"
+        "@p mbarrier.arrive.expect_tx.shared::cta.b64 t, [%1], %2;\n\t"
+        "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%3], [%4], %5, [%1];\n\t"
+        "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%6], [%7], %8, [%1];\n\t"
+        "}" ::"r"((uint32_t)pred), "r"(bar), "r"(wb + xb), "r"(dst_w), "l"(src_w), "r"(wb), "r"(dst_x), "l"(src_x), "r"(xb)
+        : "memory");
 }
 
 // d = a . b (first k-step of a block: the C operand is literal zero, no register is cleared)
@@ -127,47 +156,29 @@ __device__ __forceinline__ void consume_slot(uint32_t qaddr, uint32_t daddr, con
 // tiles (eight blocks) shares one accumulator, lane (g, c) feeding x only into column g while it
 // multiplies block g (every other lane reads a page of zeros), so that accumulator column j ends
 // up holding block j's partial product.  That leaves one scale fma per tile instead of eight,
-// and lets the nibbles go in biased, as (OFF + q): the accumulator starts at
-// -sum((OFF + 8) * x) of the column's block, computed once per block from the x the lane holds
-// anyway, so no per-pair subtraction is needed.
-//   qaddr  lane's nibble slot in tile 0 of the ring slot
-//   dsel   scales of tile c of group 0 (the lane's accumulator columns 2c, 2c+1 are that tile's blocks)
-//   xsel   per block j of a group: the x slice (+ c*16) if j == g, else the zero page (+ c*16)
-//   xown   x of the lane's own block in group 0: slice + ((g/2)*64 + (g%2)*32 + c*8) elements
+// and lets the nibbles go in biased, as (OFF + q), with no per-pair subtraction: what has to come
+// off, sum((OFF + 8) * x) of the column's block, is put into the accumulator by the tensor core
+// itself, two mma per group whose A operand is the constant -(OFF + 8) and whose B operand
+// holds block j's x in column j (each lane's own block, which it reads once per group).
+//   q, d    lane's nibble slot in tile 0 / scales of tile c, in ring slot 0
+//   xs[j]   where the lane reads the x of block j of a group: its slice if j == g, else zeros
+//   xown    x of the lane's own block in group 0
+//   soff    byte offset of the ring slot (a compile-time constant on the unrolled path)
 template <bool BF16, int CHUNK, bool FULL>
-__device__ __forceinline__ void consume_slot_m1(uint32_t qaddr, uint32_t dsel, const uint32_t (&xsel)[8], uint32_t xown,
-                                                int c, int tiles_here, float (&acc)[2]) {
+__device__ __forceinline__ void m1_consume(uint32_t q, uint32_t d, const uint32_t (&xs)[8], uint32_t xown, uint32_t soff,
+                                           int c, int tiles_here, float (&acc)[2]) {
     static_assert(CHUNK % 4 == 0, "groups of four tiles");
     constexpr int NG = CHUNK / 4;
-    constexpr float CL = BF16 ? 136.0f : 1032.0f;      // k offsets 0,1,4,5 of a nibble word
-    constexpr float CH = BF16 ? 136.0f : 72.0f;        // k offsets 2,3,6,7
+    // -(OFF + 8) as packed pairs: k offsets 0,1,4,5 of a nibble word carry OFF = 1024 (fp16) and
+    // the others 64; bf16 carries 128 everywhere
+    constexpr uint32_t NEG_LO = BF16 ? 0xC308C308u : 0xE408E408u;      // -136 | -1032
+    constexpr uint32_t NEG_HI = BF16 ? 0xC308C308u : 0xD480D480u;      // -136 | -72
     float part[NG][4];
-    bool col_ok[NG];
-    // accumulators start at -sum((OFF + 8) * x) of their block: each lane sums its own 8 k of
-    // block g, the quad adds up, and the lanes owning columns 2c, 2c+1 fetch the two totals
 #pragma unroll
     for (int grp = 0; grp < NG; ++grp) {
-        const uint4 xo = lds128(xown + grp * 4 * TILE_K * 2);
-        float2 p0, p1, p2, p3;
-        if constexpr (BF16) {
-            p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.x));
-            p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.y));
-            p2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.z));
-            p3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&xo.w));
-        } else {
-            p0 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.x));
-            p1 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.y));
-            p2 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.z));
-            p3 = __half22float2(*reinterpret_cast<const __half2 *>(&xo.w));
-        }
-        float s = CL * ((p0.x + p0.y) + (p2.x + p2.y)) + CH * ((p1.x + p1.y) + (p3.x + p3.y));
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        float c0 = -__shfl_sync(0xffffffffu, s, 8 * c);          // block 2c   lives in quad g = 2c
-        float c1 = -__shfl_sync(0xffffffffu, s, 8 * c + 4);      // block 2c+1 lives in quad g = 2c+1
-        col_ok[grp] = FULL || (grp * 4 + c) < tiles_here;        // tile c of the group exists
-        if (!col_ok[grp]) { c0 = 0.0f; c1 = 0.0f; }
-        part[grp][0] = c0; part[grp][1] = c1; part[grp][2] = c0; part[grp][3] = c1;
+        const uint4 xo = lds128(xown + soff + grp * 4 * TILE_K * 2);
+        mma16816_first<BF16>(part[grp], NEG_LO, NEG_LO, NEG_HI, NEG_HI, xo.x, xo.y);
+        mma16816_acc<BF16>(part[grp], NEG_LO, NEG_LO, NEG_HI, NEG_HI, xo.z, xo.w);
     }
     // the groups' accumulator chains are independent: step them side by side
 #pragma unroll
@@ -176,10 +187,10 @@ __device__ __forceinline__ void consume_slot_m1(uint32_t qaddr, uint32_t dsel, c
         for (int grp = 0; grp < NG; ++grp) {
             const int t = grp * 4 + t4;
             if (FULL || t < tiles_here) {
-                const uint4 qw = lds128(qaddr + t * TILE_BYTES);
+                const uint4 qw = lds128(q + soff + t * TILE_BYTES);
 #pragma unroll
                 for (int kbl = 0; kbl < TILE_KB; ++kbl) {
-                    const uint4 xv = lds128(xsel[t4 * 2 + kbl] + (t * TILE_K + kbl * QK) * 2);
+                    const uint4 xv = lds128(xs[t4 * 2 + kbl] + soff + (t * TILE_K + kbl * QK) * 2);
                     uint32_t hlo[4], hhi[4];
                     dequant_word_biased<BF16>(kbl ? qw.z : qw.x, hlo);     // column g
                     dequant_word_biased<BF16>(kbl ? qw.w : qw.y, hhi);     // column g + 8
@@ -192,12 +203,13 @@ __device__ __forceinline__ void consume_slot_m1(uint32_t qaddr, uint32_t dsel, c
     // part[.][0], [1]: output column g, blocks kb0, kb1 of tile c; [2], [3]: column g+8
 #pragma unroll
     for (int grp = 0; grp < NG; ++grp) {
-        uint2 dq = make_uint2(0u, 0u);
-        if (col_ok[grp]) dq = lds64(dsel + grp * 4 * TILE_BYTES);
-        const float2 d0 = __half22float2(*reinterpret_cast<const __half2 *>(&dq.x));   // d(kb0, g), d(kb0, g+8)
-        const float2 d1 = __half22float2(*reinterpret_cast<const __half2 *>(&dq.y));   // d(kb1, g), d(kb1, g+8)
-        acc[0] = fmaf(d0.x, part[grp][0], fmaf(d1.x, part[grp][1], acc[0]));
-        acc[1] = fmaf(d0.y, part[grp][2], fmaf(d1.y, part[grp][3], acc[1]));
+        if (FULL || (grp * 4 + c) < tiles_here) {                      // tile c of the group exists
+            const uint2 dq = lds64(d + soff + grp * 4 * TILE_BYTES);
+            const float2 d0 = __half22float2(*reinterpret_cast<const __half2 *>(&dq.x));   // d(kb0, g), d(kb0, g+8)
+            const float2 d1 = __half22float2(*reinterpret_cast<const __half2 *>(&dq.y));   // d(kb1, g), d(kb1, g+8)
+            acc[0] = fmaf(d0.x, part[grp][0], fmaf(d1.x, part[grp][1], acc[0]));
+            acc[1] = fmaf(d0.y, part[grp][2], fmaf(d1.y, part[grp][3], acc[1]));
+        }
     }
 }
 
@@ -208,7 +220,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
 
 // KS = warps of a CTA that split k for the same column tile; the CTA covers 8/KS column tiles.
 // CHUNK tiles per ring slot, SLOTS slots per warp.
-template <bool BF16, int MF, bool M1, int KS, int CHUNK, int SLOTS>
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *__restrict__ prepacked, int64_t K,
             int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add) {
@@ -217,13 +229,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     extern __shared__ __align__(128) uint8_t ring_all[];
     __shared__ __align__(8) uint64_t bars[GEMV_WARPS][SLOTS];
     __shared__ float red[GEMV_WARPS][MF][TILE_N * 8];
-    __shared__ __align__(16) uint8_t zero_page[M1 ? G::X_ROW + 64 : 16];    // what the other seven mma columns read
 
-    if constexpr (M1) {
-        for (int i = threadIdx.x * 16; i < (int)sizeof(zero_page); i += GEMV_THREADS * 16)
-            *reinterpret_cast<uint4 *>(zero_page + i) = make_uint4(0u, 0u, 0u, 0u);
-        __syncthreads();
-    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int ks = warp % KS, ntl = warp / KS;
@@ -300,12 +306,6 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     uint32_t xaddr0[MF];
 #pragma unroll
     for (int f = 0; f < MF; ++f) xaddr0[f] = ring_s + G::W_BYTES + min(f * 8 + g, M - 1) * G::X_STRIDE + c * 16;
-    // single-row path: see consume_slot_m1
-    float acc1[2] = {0.0f, 0.0f};
-    const uint32_t zero_s = smem_addr_u32(zero_page) + c * 16;
-    const uint32_t xslice0 = ring_s + G::W_BYTES + c * 16;
-    const uint32_t xown0 = ring_s + G::W_BYTES + ((g >> 1) * TILE_K + (g & 1) * QK + c * 8) * 2;
-    const uint32_t dsel0 = ring_s + c * TILE_BYTES + TILE_QS_BYTES + g * 8;
 
     int slot = 0;
     uint32_t parity = 0, soff = 0;           // soff = slot * slot_bytes
@@ -326,18 +326,8 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 #pragma unroll
         for (int f = 0; f < MF; ++f) xaddr[f] = xaddr0[f] + soff;
         const int tiles_here = ntiles - ci * CHUNK;
-        if constexpr (M1) {
-            uint32_t xsel[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) xsel[j] = (g == j) ? xslice0 + soff : zero_s;
-            if (tiles_here >= CHUNK)
-                consume_slot_m1<BF16, CHUNK, true>(qaddr0 + soff, dsel0 + soff, xsel, xown0 + soff, c, CHUNK, acc1);
-            else
-                consume_slot_m1<BF16, CHUNK, false>(qaddr0 + soff, dsel0 + soff, xsel, xown0 + soff, c, tiles_here, acc1);
-        } else {
-            if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(qaddr0 + soff, daddr0 + soff, xaddr, CHUNK, acc);
-            else consume_slot<BF16, MF, CHUNK, false>(qaddr0 + soff, daddr0 + soff, xaddr, tiles_here, acc);
-        }
+        if (tiles_here >= CHUNK) consume_slot<BF16, MF, CHUNK, true>(qaddr0 + soff, daddr0 + soff, xaddr, CHUNK, acc);
+        else consume_slot<BF16, MF, CHUNK, false>(qaddr0 + soff, daddr0 + soff, xaddr, tiles_here, acc);
         __syncwarp();                    // every lane has consumed the slot before it is refilled
         if (ci + SLOTS < nchunks) {
             if (lane == 0) issue_w(ci + SLOTS, slot);
@@ -347,21 +337,9 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
         if (++slot == SLOTS) { slot = 0; soff = 0; parity ^= 1; }
     }
 
-    if constexpr (M1) {
-        // each lane of a quad summed different blocks of output columns g and g+8
-        float a0 = acc1[0], a1 = acc1[1];
-        a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
-        a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-        a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
-        a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
-        if (c == 0) {
-            red[warp][0][g] = a0;
-            red[warp][0][g + 8] = a1;
-        }
-    }
     // acc[f][0..1] = column g, rows f*8 + 2c, 2c+1 ; acc[f][2..3] = column g+8, same rows
 #pragma unroll
-    for (int f = 0; f < (M1 ? 0 : MF); ++f) {
+    for (int f = 0; f < MF; ++f) {
         red[warp][f][(2 * c) * TILE_N + g] = acc[f][0];
         red[warp][f][(2 * c + 1) * TILE_N + g] = acc[f][1];
         red[warp][f][(2 * c) * TILE_N + g + 8] = acc[f][2];
@@ -384,7 +362,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
     }
 }
 
-template <bool BF16, int MF, bool M1, int KS, int CHUNK, int SLOTS>
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
 static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
                        int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
     constexpr int NTC = GEMV_WARPS / KS;
@@ -394,7 +372,7 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, M1, KS, CHUNK, SLOTS>,
+        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(MF * 8)));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
@@ -409,8 +387,234 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
-    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, M1, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
                                     (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add));
+    return Q4B_OK;
+}
+
+// ---- single activation row ---------------------------------------------------------------
+// Same decomposition as gemv_kernel (a warp per column tile and k range, a private ring per
+// warp, warps of a CTA that share a column tile reduced through shared memory), with the slot
+// loop unrolled over the ring so that every shared-memory address is a per-lane register plus a
+// compile-time offset, and with refills that cost a handful of 32-bit instructions.
+template <int CHUNK, int SLOTS> struct M1Geom {
+    static constexpr int W_BYTES = CHUNK * TILE_BYTES;
+    static constexpr int X_BYTES = CHUNK * TILE_K * 2;            // the chunk's slice of the activation row
+    static constexpr int SLOT_BYTES = W_BYTES + X_BYTES;
+    static constexpr int RING_BYTES = GEMV_WARPS * SLOTS * SLOT_BYTES;
+    // Zero pages, one per ring position and SLOT_BYTES apart, so that "zero page + slot offset"
+    // is a zero page again: a lane's eight x addresses then do not depend on the slot.
+    static constexpr int ZERO_BYTES = (SLOTS - 1) * SLOT_BYTES + X_BYTES;
+};
+
+template <bool BF16, int KS, int CHUNK, int SLOTS>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepacked, int64_t K, int64_t N,
+               uint16_t *__restrict__ y, const float *__restrict__ addend) {
+    using G = M1Geom<CHUNK, SLOTS>;
+    constexpr int NTC = GEMV_WARPS / KS;
+    extern __shared__ __align__(128) uint8_t ring_all[];
+    __shared__ __align__(16) uint8_t zero_region[G::ZERO_BYTES];
+    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][SLOTS];
+    __shared__ float red[GEMV_WARPS][TILE_N];
+
+#ifdef Q4B_GEMV_TRACE
+    unsigned long long trace_t[4] = {0, 0, 0, 0};
+#endif
+    TRACE_STAMP(0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int ks = warp % KS, ntl = warp / KS;
+    const int NT = (int)tiles_n(N);
+    const int KU = (int)tiles_k(K);
+    const int nt = (int)blockIdx.x * NTC + ntl;
+    const bool active = nt < NT;
+    const int ku0 = KU * ks / KS, ku1 = KU * (ks + 1) / KS;
+    const int ntiles = active ? ku1 - ku0 : 0;
+    const int nfull = ntiles / CHUNK;                          // chunks with all CHUNK tiles
+    const int nchunks = (ntiles + CHUNK - 1) / CHUNK;
+    const int xelems = (int)(min((int64_t)ku1 * TILE_K, K) - (int64_t)ku0 * TILE_K);   // x this warp multiplies
+
+    const uint32_t ring_s = smem_addr_u32(ring_all) + (uint32_t)(warp * SLOTS * G::SLOT_BYTES);
+    const uint32_t bar_s = smem_addr_u32(&bars[warp][0]);
+    const uint8_t *wsrc = prepacked + tile_offset(active ? nt : 0, ku0, KU);
+    const uint16_t *xsrc = x + (int64_t)ku0 * TILE_K;
+
+    // Refill of ring position `slot` with chunk `ci` (lane 0 only): the barrier is armed with the
+    // bytes of both copies, so it cannot complete before the activation slice has landed too.
+    auto chunk_tiles = [&](int ci) { return min(CHUNK, ntiles - ci * CHUNK); };
+    auto chunk_x_bytes = [&](int ci) { return (uint32_t)(min(CHUNK * TILE_K, xelems - ci * CHUNK * TILE_K) * 2); };
+    auto issue_w = [&](int ci, int slot) {
+        const uint32_t wb = (uint32_t)(chunk_tiles(ci) * TILE_BYTES);
+        mbar_expect_tx(bar_s + 8u * slot, wb + chunk_x_bytes(ci));
+        bulk_g2s(ring_s + (uint32_t)(slot * G::SLOT_BYTES), wsrc + (size_t)ci * G::W_BYTES, wb, bar_s + 8u * slot);
+    };
+    auto issue_x = [&](int ci, int slot) {
+        bulk_g2s(ring_s + (uint32_t)(slot * G::SLOT_BYTES + G::W_BYTES), xsrc + (size_t)ci * CHUNK * TILE_K,
+                 chunk_x_bytes(ci), bar_s + 8u * slot);
+    };
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s + 8u * s) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s)
+            if (s < nchunks) issue_w(s, s);
+    }
+    // zero pages (what the other seven mma columns read)
+    for (int i = threadIdx.x * 16; i < SLOTS * G::X_BYTES; i += GEMV_THREADS * 16)
+        *reinterpret_cast<uint4 *>(zero_region + (i / G::X_BYTES) * G::SLOT_BYTES + (i % G::X_BYTES)) =
+            make_uint4(0u, 0u, 0u, 0u);
+    if (K % TILE_K) {
+        // Odd number of 32-k blocks: the last tile's pad block has zero weights, but what it is
+        // multiplied with must be finite, so the x slices start out as zeros.
+        for (int s = 0; s < SLOTS; ++s)
+            for (int i = lane * 16; i < G::X_BYTES; i += 32 * 16)
+                *reinterpret_cast<uint4 *>(ring_all + (size_t)(warp * SLOTS + s) * G::SLOT_BYTES + G::W_BYTES + i) =
+                    make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // Weights never depend on earlier kernels of the stream; x and y do.  Under programmatic
+    // dependent launch the weight copies above overlap the previous kernel's tail.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    TRACE_STAMP(1);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s)
+            if (s < nchunks) issue_x(s, s);
+    }
+
+    // per-lane shared-memory addresses inside ring position 0
+    const uint32_t q0 = ring_s + slot_of(g, c) * 16;
+    const uint32_t d0 = ring_s + c * TILE_BYTES + TILE_QS_BYTES + g * 8;
+    const uint32_t xslice = ring_s + G::W_BYTES + c * 16;
+    const uint32_t xown = ring_s + G::W_BYTES + ((g >> 1) * TILE_K + (g & 1) * QK + c * 8) * 2;
+    const uint32_t zero_s = smem_addr_u32(zero_region) + c * 16;
+    uint32_t xs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xs[j] = (g == j) ? xslice : zero_s;
+
+    float acc[2] = {0.0f, 0.0f};
+    auto wait_slot = [&](uint32_t bar, uint32_t parity) -> bool {
+        uint32_t done;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (!done) {                     // slow path: bounded polling
+            int spins = 0;
+            while (!done && ++spins <= GEMV_SPIN_LIMIT)
+                asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+            if (!done) atomicCAS(&g_wait_status, 0, 101);
+        }
+        return __all_sync(0xffffffffu, done != 0);
+    };
+
+    {
+        uint32_t parity = 0;
+        int ci = 0;
+        bool ok = true;
+        const int nfast = xelems / (CHUNK * TILE_K);           // chunks whose weights and x slice are both whole
+        const uint8_t *wnext = wsrc + (size_t)SLOTS * G::W_BYTES;      // chunk ci + SLOTS
+        const uint16_t *xnext = xsrc + (size_t)SLOTS * CHUNK * TILE_K;
+        while (ok && ci < nfull) {
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                if (ok && ci < nfull) {
+                    ok = wait_slot(bar_s + 8u * s, parity);
+#ifdef Q4B_GEMV_TRACE
+                    if (threadIdx.x == 0 && trace_t[2] == 0) trace_t[2] = trace_now();
+#endif
+                    if (ok) {
+                        m1_consume<BF16, CHUNK, true>(q0, d0, xs, xown, (uint32_t)(s * G::SLOT_BYTES), c, CHUNK, acc);
+                        __syncwarp();            // every lane has read the slot before it is refilled
+                        const uint32_t dst = ring_s + (uint32_t)(s * G::SLOT_BYTES);
+                        if (ci + SLOTS < nfast)
+                            refill_pred(lane == 0, bar_s + 8u * s, dst, wnext, G::W_BYTES, dst + G::W_BYTES, xnext, G::X_BYTES);
+                        else if (ci + SLOTS < nchunks)
+                            refill_pred(lane == 0, bar_s + 8u * s, dst, wnext, (uint32_t)(chunk_tiles(ci + SLOTS) * TILE_BYTES),
+                                        dst + G::W_BYTES, xnext, chunk_x_bytes(ci + SLOTS));
+                        wnext += G::W_BYTES;
+                        xnext += CHUNK * TILE_K;
+                        ++ci;
+                    }
+                }
+            }
+            parity ^= 1;
+        }
+        if (ok && nchunks > nfull) {             // the k range's last, partial chunk
+            const int s = nfull % SLOTS;
+            if (wait_slot(bar_s + 8u * s, (uint32_t)((nfull / SLOTS) & 1)))
+                m1_consume<BF16, CHUNK, false>(q0, d0, xs, xown, (uint32_t)(s * G::SLOT_BYTES), c, ntiles - nfull * CHUNK, acc);
+        }
+    }
+
+    // each lane of a quad summed different blocks of output columns g and g+8
+    float a0 = acc[0], a1 = acc[1];
+    a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+    a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+    if (c == 0) {
+        red[warp][g] = a0;
+        red[warp][g + 8] = a1;
+    }
+    __syncthreads();
+    if (threadIdx.x < NTC * TILE_N) {
+        const int tl = threadIdx.x / TILE_N, nl = threadIdx.x % TILE_N;
+        const int n = ((int)blockIdx.x * NTC + tl) * TILE_N + nl;
+        if (n < N) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < KS; ++j) sum += red[tl * KS + j][nl];
+            if (addend != nullptr) sum += addend[n];           // fp32 term added before the one rounding
+            y[n] = out_bits<BF16>(sum);
+        }
+    }
+#ifdef Q4B_GEMV_TRACE
+    TRACE_STAMP(3);
+    if (threadIdx.x == 0) {
+        const unsigned int i = atomicAdd(&g_trace_n, 1u);
+        if (i < (unsigned)TRACE_MAX) {
+            unsigned int smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            g_trace[i * 6 + 0] = (unsigned long long)prepacked;
+            g_trace[i * 6 + 1] = (unsigned long long)blockIdx.x | ((unsigned long long)smid << 32);
+            for (int j = 0; j < 4; ++j) g_trace[i * 6 + 2 + j] = trace_t[j];
+        }
+    }
+#endif
+}
+
+template <bool BF16, int KS, int CHUNK, int SLOTS>
+static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend,
+                          int flags, cudaStream_t st) {
+    using G = M1Geom<CHUNK, SLOTS>;
+    constexpr int NTC = GEMV_WARPS / KS;
+    // opt in to > 48 KB of dynamic shared memory once per device and instantiation
+    static bool attr_done[64] = {};
+    int dev = 0;
+    Q4B_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_m1_kernel<BF16, KS, CHUNK, SLOTS>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, G::RING_BYTES));
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(tiles_n(N), NTC));
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = (size_t)G::RING_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_m1_kernel<BF16, KS, CHUNK, SLOTS>, (const uint16_t *)x,
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend));
     return Q4B_OK;
 }
 
@@ -420,24 +624,33 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
 int device_sm_count();
 int gemv_geom_override();
 
+// Single-row launches: k-split and ring geometry by the number of column tiles NT.  A chain of
+// decode launches runs fastest when each is one wave of CTAs (the next launch's CTAs then load
+// their weights while this one computes, and no late wave starts cold), made of as few and as
+// long-lived CTAs as still fill the SMs:
+//   NT <= 2 SMs : k-split 8, 8 tiles x 2 slots (2 CTAs per SM)     NT <= 4 SMs : k-split 4, same ring
+//   NT <= 6 SMs : k-split 4, 4 tiles x 3 slots (3 CTAs per SM)     beyond      : k-split 4, 4 x 2 (4 per SM)
+static int m1_ksplit(int64_t NT, int sms) { return NT <= 2LL * sms ? 8 : 4; }
+static int m1_geometry(int64_t NT, int ks, int sms) {
+    const int64_t grid = ceil_div(NT, GEMV_WARPS / ks);
+    if (grid <= 2LL * sms) return 82;
+    if (grid <= 3LL * sms) return 43;
+    return 42;
+}
+
 template <bool BF16, int KS>
 static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
                          int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
     if (M == 1) {
-        // one row: the eight mma columns carry eight 32-k blocks (see consume_slot_m1)
-        switch (gemv_geom_override()) {
-            case 43: return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 42: return launch_gemv<BF16, 1, true, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 44: return launch_gemv<BF16, 1, true, KS, 4, 4>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 82: return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 83: return launch_gemv<BF16, 1, true, KS, 8, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            default: break;
+        // one row: the eight mma columns carry eight 32-k blocks (see m1_consume)
+        int geom = m1_geometry(tiles_n(N), KS, device_sm_count());
+        if (const int o = gemv_geom_override()) geom = o;
+        switch (geom) {
+            case 43: return launch_gemv_m1<BF16, KS, 4, 3>(x, prepacked, K, N, y, addend, flags, st);
+            case 42: return launch_gemv_m1<BF16, KS, 4, 2>(x, prepacked, K, N, y, addend, flags, st);
+            case 44: return launch_gemv_m1<BF16, KS, 4, 4>(x, prepacked, K, N, y, addend, flags, st);
+            default: return launch_gemv_m1<BF16, KS, 8, 2>(x, prepacked, K, N, y, addend, flags, st);
         }
-        const int64_t grid = ceil_div(tiles_n(N), GEMV_WARPS / KS);
-        const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
-        if (tiles_per_warp <= 8 && grid > 2LL * device_sm_count())
-            return launch_gemv<BF16, 1, true, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-        return launch_gemv<BF16, 1, true, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
     }
     if (M <= 4) {
         // 8 tiles x 2 slots keeps more bytes in flight per warp (2 CTAs per SM); 4 tiles x 3 slots
@@ -447,11 +660,11 @@ static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacke
         const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
         int geom = (tiles_per_warp <= 8 && grid > 2LL * device_sm_count()) ? 43 : 82;
         if (const int o = gemv_geom_override()) geom = o;
-        if (geom == 82) return launch_gemv<BF16, 1, false, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-        return launch_gemv<BF16, 1, false, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        if (geom == 82) return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
     }
-    if (M <= 8) return launch_gemv<BF16, 1, false, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-    return launch_gemv<BF16, 2, false, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    if (M <= 8) return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
 }
 
 template <bool BF16>
@@ -484,6 +697,20 @@ int gemv_wait_status(int *value) {
 
 using namespace q4b;
 
+#ifdef Q4B_GEMV_TRACE
+// copies the trace records out (returns their number) and clears the trace
+extern "C" __attribute__((visibility("default"))) int q4b_debug_gemv_trace(unsigned long long *out, int max_records) {
+    unsigned int n = 0;
+    if (cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n)) != cudaSuccess) return -1;
+    if (n > (unsigned)TRACE_MAX) n = TRACE_MAX;
+    if ((int)n > max_records) n = (unsigned)max_records;
+    if (n && cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 6 * n) != cudaSuccess) return -1;
+    const unsigned int zero = 0;
+    cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
+    return (int)n;
+}
+#endif
+
 extern "C" int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                         int64_t N, void *y, int64_t ldy, int flags, void *stream) {
     return q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y, ldy, flags, stream);
@@ -501,6 +728,7 @@ extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     // k-split: as few splits as still give every SM several CTAs, never more splits than tiles
     const int64_t NT = tiles_n(N), KU = tiles_k(K);
     int ks = gemv_ksplit_override();
+    if (ks == 0 && M == 1) ks = m1_ksplit(NT, device_sm_count());
     if (ks == 0) {
         const int64_t want = 4LL * device_sm_count();
         ks = 8;
