@@ -325,7 +325,7 @@ def run_ours(args) -> None:
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "frac_of_nominal_8tbs": per_gpu / 8000.0,
-                         "kernel": "gemv_kernel", "launches": launches_per_step * args.steps,
+                         "kernel": "gemv_m1_kernel", "launches": launches_per_step * args.steps,
                          "avg_launch_us": ms * 1e3 / (launches_per_step * args.steps),
                          "traffic": (traffic.get("gemv_dram_bytes_per_algorithmic_byte") or 0) * step_bytes / launches_per_step
                          if traffic.get("gemv_dram_bytes_per_algorithmic_byte") else None},

@@ -69,7 +69,12 @@ enum {
     /* Launch with programmatic dependent launch: the kernel may start fetching WEIGHTS while
      * earlier work on the stream is still running, and waits for that work before it reads x
      * or writes y.  Only valid when nothing still in flight on the stream writes `prepacked`. */
-    Q4B_FLAG_PDL = 1
+    Q4B_FLAG_PDL = 1,
+    /* M = 1 only: run the decode on the 5th-generation tensor cores, weights dequantised into
+     * tensor memory (tcgen05.st / tcgen05.mma), instead of the default mma.sync kernel.  Same
+     * results within the path's tolerance; measured slower on the shapes benchmarked so far, kept
+     * selectable for comparison.  Ignored (default kernel used) for shapes it does not cover. */
+    Q4B_FLAG_DECODE_TMEM = 2
 };
 
 Q4B_API const char *q4b_strerror(int status);

@@ -69,6 +69,16 @@ int gemv_geom_override() {
     return v;
 }
 
+// Q4B_GEMV_TC=0/1 forces the tensor-memory decode kernel off / on for M = 1 (benchmark sweeps only).
+int gemv_tc_override() {
+    static int v = -2;
+    if (v == -2) {
+        const char *e = getenv("Q4B_GEMV_TC");
+        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
+    }
+    return v;
+}
+
 }  // namespace q4b
 
 using namespace q4b;

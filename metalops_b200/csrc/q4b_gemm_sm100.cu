@@ -130,6 +130,12 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag, code));
 #endif
 }
+// true on one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
@@ -267,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                 const int mt = t % num_mt;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!mbar_wait(bar_empty_a(a.s), a.phase ^ 1, abort_flag, 1)) goto done;
-                    mbar_arrive_expect_tx(bar_full_a(a.s), (uint32_t)A_BYTES);
+                    mbar_arrive_expect_tx(bar_full_a(a.s), (uint32_t)(M <= HALF_M ? A_HALF_BYTES : A_BYTES));
                     tma_load_2d(base + SMEM_A + a.s * A_BYTES, &tmap_x, ks * BK, mt * BM, bar_full_a(a.s));
                     a.advance(SA);
                 }
@@ -295,7 +301,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         }
     } else if (warp == WARP_MMA) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // The whole warp runs the loop, converged, and one elected lane issues: the operands of
+        // tcgen05.mma then live in uniform registers instead of being moved there per instruction.
+        {
             const uint32_t idesc = make_idesc(BF16, HALF_M, bn);
             RingPos a, b;
             uint32_t tphase = 0;
@@ -306,29 +314,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 const int mt = t % num_mt;
                 const int halves = (M - mt * BM > HALF_M) ? 2 : 1;     // skip an all-padding lower half
-                { PROF_T0(); if (!mbar_wait(bar_tempty, tphase ^ 1, abort_flag, 2)) goto done; PROF_ADD(0); }
+                { PROF_T0(); if (!mbar_wait_warp(bar_tempty, tphase ^ 1, abort_flag, 2, lane)) goto done; PROF_ADD(0); }
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    { PROF_T0(); if (!mbar_wait(bar_full_a(a.s), a.phase, abort_flag, 3)) goto done; PROF_ADD(1); }
-                    { PROF_T0(); if (!mbar_wait(bar_full_b(b.s), b.phase, abort_flag, 4)) goto done; PROF_ADD(2); }
+                    { PROF_T0(); if (!mbar_wait_warp(bar_full_a(a.s), a.phase, abort_flag, 3, lane)) goto done; PROF_ADD(1); }
+                    { PROF_T0(); if (!mbar_wait_warp(bar_full_b(b.s), b.phase, abort_flag, 4, lane)) goto done; PROF_ADD(2); }
                     tc_fence_after();
-                    const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + b.s * B_BYTES);
-                    for (int h = 0; h < halves; ++h) {
-                        const uint64_t adesc = make_kmajor_sw128_desc(base + SMEM_A + a.s * A_BYTES + h * A_HALF_BYTES);
+                    if (elect_one()) {
+                        const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + b.s * B_BYTES);
+                        for (int h = 0; h < halves; ++h) {
+                            const uint64_t adesc = make_kmajor_sw128_desc(base + SMEM_A + a.s * A_BYTES + h * A_HALF_BYTES);
 #pragma unroll
-                        for (int k = 0; k < BK / 16; ++k)                 // +32 bytes per k16 inside the swizzle atom
-                            tc_mma_f16(tmem_base + (uint32_t)(h * BN), adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                            for (int k = 0; k < BK / 16; ++k)             // +32 bytes per k16 inside the swizzle atom
+                                tc_mma_f16(tmem_base + (uint32_t)(h * BN), adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                        }
+                        tc_commit(bar_empty_a(a.s));
+                        tc_commit(bar_empty_b(b.s));
+                        if (ks == k_steps - 1) tc_commit(bar_tfull);
                     }
-                    tc_commit(bar_empty_a(a.s));
-                    tc_commit(bar_empty_b(b.s));
+                    __syncwarp();
                     a.advance(SA);
                     b.advance(SB);
                 }
-                tc_commit(bar_tfull);
                 tphase ^= 1;
             }
 #ifdef Q4B_GEMM_PROFILE
-            if (blockIdx.x < 148) {
+            if (lane == 0 && blockIdx.x < 148) {
                 g_gemm_prof[blockIdx.x * 8 + 0] = prof[0];
                 g_gemm_prof[blockIdx.x * 8 + 1] = prof[1];
                 g_gemm_prof[blockIdx.x * 8 + 2] = prof[2];
@@ -504,7 +515,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
     const int mt = (M + BM - 1) / BM;
     int bn = BN;
     long best = -1;
-    for (int cand = BN; cand >= 128; cand -= 32) {
+    for (int cand = BN; cand >= 32; cand -= 32) {
         const long t = (long)mt * ((N + cand - 1) / cand);
         const long cost = ((t + sms - 1) / sms) * (cand + 24);
         if (best < 0 || cost < best) { best = cost; bn = cand; }
@@ -524,6 +535,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
 
 int device_sm_count();
 int gemv_wait_status(int *value);
+int gemv_tc_wait_status(int *value);
 
 }  // namespace q4b
 
@@ -551,7 +563,8 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)gemm::BM};   // 64 k x 256 rows per copy
+    // 64 k x 256 rows per copy; a single half tile (M <= 128) is copied as 128 rows
+    const cuuint32_t box[2] = {(cuuint32_t)gemm::BK, (cuuint32_t)(M <= gemm::HALF_M ? gemm::HALF_M : gemm::BM)};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&tmap, x_dtype == Q4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                      const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -580,6 +593,8 @@ extern "C" int q4b_wait_status(void *stream, int *detail) {
         Q4B_CUDA_TRY(cudaMemcpyToSymbol(gemm::g_gemm_status, &zero, sizeof(int)));
     }
     if (int rc = gemv_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = gemv_tc_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (detail) *detail = h;
     return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;

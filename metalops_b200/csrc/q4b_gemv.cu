@@ -680,6 +680,10 @@ static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const v
 
 int device_sm_count();
 int gemv_ksplit_override();
+int gemv_tc_override();
+int gemv_tc_ksplit(int64_t K, int64_t N, int sms);
+int gemv_tc_launch(const void *x, int bf16, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend, int ks,
+                   int flags, cudaStream_t st);
 
 // read and clear this file's wait status (host side; the caller has synchronised the stream)
 int gemv_wait_status(int *value) {
@@ -736,6 +740,10 @@ extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     }
     while (ks > 1 && KU < ks) ks /= 2;
     cudaStream_t st = (cudaStream_t)stream;
+    if (M == 1 && (gemv_tc_override() == 1 || ((flags & Q4B_FLAG_DECODE_TMEM) && gemv_tc_override() != 0))) {
+        const int tks = gemv_tc_ksplit(K, N, device_sm_count());
+        if (tks > 0) return gemv_tc_launch(x, x_dtype == Q4B_BF16, prepacked, K, N, y, addend, tks, flags, st);
+    }
     return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st)
                                : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
 }

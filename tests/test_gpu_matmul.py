@@ -228,3 +228,25 @@ def test_config5_gemm_sweep(mo, cuda_dev, M):
     cols = torch.randperm(14336, generator=g)[:2048].sort().values
     ref = c_oracle.matmul_f32(x[rows].contiguous(), blocks[:, cols.to(cuda_dev)].cpu().contiguous())
     assert orc.rel_l2(y[rows.to(cuda_dev)][:, cols.to(cuda_dev)], ref) <= TOL_F16
+
+
+@pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 4096), (4096, 11008), (1056, 200), (96, 16)])
+def test_decode_tensor_memory_kernel(mo, cuda_dev, K, N, xdtype):
+    """M = 1 on the tcgen05 / tensor-memory decode kernel (selected by flag): same tolerance,
+    bitwise repeatable, no bounded wait gave up.  Covers a k split across a thread-block
+    cluster, a panel with fewer than eight column tiles and an odd number of 32-k blocks."""
+    from metalops_b200 import _cabi, quantization as Q
+    w, x = make_case(4000 + K + N, 1, K, N, xdtype)
+    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+    pre = mo.prepack_ggml_q4_0(blocks)
+    y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv", flags=_cabi.FLAG_DECODE_TMEM)
+    assert Q.wait_status(cuda_dev) == 0
+    ref = c_oracle.matmul_f32(x, blocks.cpu())
+    assert torch.isfinite(y).all()
+    assert orc.rel_l2(y, ref) <= TOL
+    y2 = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv", flags=_cabi.FLAG_DECODE_TMEM)
+    assert torch.equal(y, y2), "two runs differ bitwise"
+    # the default kernel agrees to well within the tolerance
+    y_default = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv")
+    assert orc.rel_l2(y, y_default.float().cpu()) <= TOL
