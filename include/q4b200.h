@@ -74,7 +74,12 @@ enum {
      * tensor memory (tcgen05.st / tcgen05.mma), instead of the default mma.sync kernel.  Same
      * results within the path's tolerance; measured slower on the shapes benchmarked so far, kept
      * selectable for comparison.  Ignored (default kernel used) for shapes it does not cover. */
-    Q4B_FLAG_DECODE_TMEM = 2
+    Q4B_FLAG_DECODE_TMEM = 2,
+    /* M > 128 only: run the prefill on CTA pairs (tcgen05.mma.cta_group::2, each CTA of a two-CTA
+     * cluster loads half of the X tile and dequantises half of the tile's columns) instead of the
+     * default one-CTA kernel.  Same results within the path's tolerance; measured equal or slower
+     * on the shapes benchmarked so far, kept selectable for comparison. */
+    Q4B_FLAG_GEMM_PAIR = 4
 };
 
 Q4B_API const char *q4b_strerror(int status);

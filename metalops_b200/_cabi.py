@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libq4b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
-FLAG_NONE, FLAG_PDL, FLAG_DECODE_TMEM = 0, 1, 2
+FLAG_NONE, FLAG_PDL, FLAG_DECODE_TMEM, FLAG_GEMM_PAIR = 0, 1, 2, 4
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_ARCH, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(9)
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}

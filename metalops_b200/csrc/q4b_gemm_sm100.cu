@@ -536,6 +536,18 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
 int device_sm_count();
 int gemv_wait_status(int *value);
 int gemv_tc_wait_status(int *value);
+int gemm2_wait_status(int *value);
+int gemm2_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int K, int N, const float *addend,
+                 int64_t ld_add, void *y, int64_t ldy, cudaStream_t st);
+// Q4B_GEMM_PAIR=0/1 forces the CTA-pair prefill kernel off / on (benchmark sweeps only)
+static int gemm_pair_override() {
+    static int v = -2;
+    if (v == -2) {
+        const char *e = getenv("Q4B_GEMM_PAIR");
+        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
+    }
+    return v;
+}
 
 }  // namespace q4b
 
@@ -549,7 +561,6 @@ extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
 extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                                int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
                                void *stream) {
-    (void)flags;
     if (addend != nullptr && ld_add < N) return Q4B_ERR_ARG;
     if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
@@ -557,6 +568,9 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
     if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
     if (q4b_device_ok() != Q4B_OK) return Q4B_ERR_ARCH;
+    if (gemm_pair_override() == 1 || ((flags & Q4B_FLAG_GEMM_PAIR) && gemm_pair_override() != 0 && M > gemm::HALF_M))
+        return gemm2_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, (int)K, (int)N, addend, ld_add, y, ldy,
+                            (cudaStream_t)stream);
     gemm::EncodeTiledFn enc = gemm::get_encode_fn();
     if (enc == nullptr) return Q4B_ERR_CUDA;
 
@@ -595,6 +609,8 @@ extern "C" int q4b_wait_status(void *stream, int *detail) {
     if (int rc = gemv_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (int rc = gemv_tc_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = gemm2_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (detail) *detail = h;
     return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;

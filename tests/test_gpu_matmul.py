@@ -250,3 +250,24 @@ def test_decode_tensor_memory_kernel(mo, cuda_dev, K, N, xdtype):
     # the default kernel agrees to well within the tolerance
     y_default = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv")
     assert orc.rel_l2(y, y_default.float().cpu()) <= TOL
+
+
+@pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N", [(129, 96, 48), (300, 1024, 1000), (512, 512, 512), (2048, 4096, 1024), (1000, 2080, 4112)])
+def test_prefill_cta_pair_kernel(mo, cuda_dev, M, K, N, xdtype):
+    """The cta_group::2 prefill kernel (selected by flag): same tolerance, bitwise repeatable, no
+    bounded wait gave up.  Covers row and column tails, a second CTA whose column half lies wholly
+    beyond N, an odd number of 32-k blocks and several tiles per CTA pair."""
+    from metalops_b200 import _cabi, quantization as Q
+    w, x = make_case(5000 + M + K + N, M, K, N, xdtype)
+    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+    pre = mo.prepack_ggml_q4_0(blocks)
+    y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm", flags=_cabi.FLAG_GEMM_PAIR)
+    assert Q.wait_status(cuda_dev) == 0
+    ref = c_oracle.matmul_f32(x, blocks.cpu())
+    assert torch.isfinite(y).all()
+    assert orc.rel_l2(y, ref) <= TOL
+    y2 = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm", flags=_cabi.FLAG_GEMM_PAIR)
+    assert torch.equal(y, y2), "two runs differ bitwise"
+    y_default = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm")
+    assert orc.rel_l2(y, y_default.float().cpu()) <= TOL
