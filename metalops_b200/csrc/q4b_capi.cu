@@ -64,7 +64,7 @@ int gemv_geom_override() {
     if (v < 0) {
         const char *e = getenv("Q4B_GEMV_GEOM");
         const int k = e ? atoi(e) : 0;
-        v = (k == 82 || k == 43 || k == 42 || k == 44 || k == 83) ? k : 0;
+        v = (k == 82 || k == 43 || k == 42 || k == 44 || k == 83 || k == 22 || k == 23) ? k : 0;
     }
     return v;
 }

@@ -652,18 +652,25 @@ static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacke
             default: return launch_gemv_m1<BF16, KS, 8, 2>(x, prepacked, K, N, y, addend, flags, st);
         }
     }
-    if (M <= 4) {
-        // 8 tiles x 2 slots keeps more bytes in flight per warp (2 CTAs per SM); 4 tiles x 3 slots
-        // fits 3 CTAs per SM, which wins when warps are short (<= 8 tiles) and the grid is several
-        // waves of CTAs.
-        const int64_t grid = ceil_div(tiles_n(N), GEMV_WARPS / KS);
-        const int64_t tiles_per_warp = ceil_div(tiles_k(K), KS);
-        int geom = (tiles_per_warp <= 8 && grid > 2LL * device_sm_count()) ? 43 : 82;
+    // Several rows: slot bytes grow with M (the slot carries the rows' x slices), so the ring gets
+    // shorter as M grows.  geom = <tiles per slot><slots>; measured best per M over the Llama-shaped
+    // layers: two rows like one row (one wave of CTAs where the ring allows it), 3..8 rows 4 tiles
+    // x 2 slots (4 CTAs per SM), more rows 2 x 2.
+    int geom = M <= 8 ? 42 : 22;
+    if (M == 2) geom = m1_geometry(tiles_n(N), KS, device_sm_count());
+    if (M <= 8) {
         if (const int o = gemv_geom_override()) geom = o;
-        if (geom == 82) return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-        return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        switch (geom) {
+            case 82: return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 43: return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 23: return launch_gemv<BF16, 1, KS, 2, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 22: return launch_gemv<BF16, 1, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            default: return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        }
     }
-    if (M <= 8) return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    if (const int o = gemv_geom_override()) geom = o;
+    if (geom == 23) return launch_gemv<BF16, 2, KS, 2, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    if (geom == 42) return launch_gemv<BF16, 2, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
     return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
 }
 
@@ -729,15 +736,10 @@ extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     if (M > 16 || K % QK || tiles_k(K) > (1 << 24)) return Q4B_ERR_SHAPE;
     if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
     if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
-    // k-split: as few splits as still give every SM several CTAs, never more splits than tiles
+    // k-split (see m1_ksplit for one row), never more splits than k-tiles
     const int64_t NT = tiles_n(N), KU = tiles_k(K);
     int ks = gemv_ksplit_override();
-    if (ks == 0 && M == 1) ks = m1_ksplit(NT, device_sm_count());
-    if (ks == 0) {
-        const int64_t want = 4LL * device_sm_count();
-        ks = 8;
-        while (ks > 1 && ceil_div(NT, GEMV_WARPS / (ks / 2)) >= want) ks /= 2;
-    }
+    if (ks == 0) ks = M == 1 ? m1_ksplit(NT, device_sm_count()) : 8;     // several rows: always 8 (measured)
     while (ks > 1 && KU < ks) ks /= 2;
     cudaStream_t st = (cudaStream_t)stream;
     if (M == 1 && (gemv_tc_override() == 1 || ((flags & Q4B_FLAG_DECODE_TMEM) && gemv_tc_override() != 0))) {
