@@ -79,7 +79,12 @@ enum {
      * cluster loads half of the X tile and dequantises half of the tile's columns) instead of the
      * default one-CTA kernel.  Same results within the path's tolerance; measured equal or slower
      * on the shapes benchmarked so far, kept selectable for comparison. */
-    Q4B_FLAG_GEMM_PAIR = 4
+    Q4B_FLAG_GEMM_PAIR = 4,
+    /* Activation applied to the fp32 result (after the addend, before the one rounding), as the
+     * reference's fused kernels matmul_int4_silu / matmul_int4_gelu do (quant_kernels.metal:880-1144):
+     * SiLU v / (1 + exp(-v)), or GELU in its tanh form.  At most one of the two. */
+    Q4B_FLAG_ACT_SILU = 8,
+    Q4B_FLAG_ACT_GELU = 16
 };
 
 Q4B_API const char *q4b_strerror(int status);
@@ -181,10 +186,20 @@ Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
                              int64_t K, int64_t N, int64_t group, float *addend_out, void *stream);
 
 /*
+ * RMSNorm in front of a quantised linear layer, the first step of the reference's
+ * fused_rmsnorm_linear_int4 (core_mps.mm:3017-3103; kernel training_kernels.metal:425-485):
+ * y[m, :] = T(float(x[m, :]) * rsqrt(mean(x[m, :]^2) + eps) * float(weight[:])), sums in fp32.
+ * x, weight and y share `dtype` (Q4B_F16 or Q4B_BF16); y may not alias x.
+ */
+Q4B_API int q4b_rmsnorm(const void *x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                        const void *weight, float eps, void *y, int64_t ldy, void *stream);
+
+/*
  * The matmul kernels bound every mbarrier wait; a wait that gives up makes the kernel set a
  * status word on the device and stop early (its output is then incomplete).  This call
  * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with
- * *detail (may be NULL) = which wait gave up (1..6 prefill kernel roles, 100 decode kernel).
+ * *detail (may be NULL) = which wait gave up (1..8 prefill kernel roles, 100-102 decode kernels,
+ * 201-206 tensor-memory decode kernel, 301-309 CTA-pair prefill kernel).
  * It never traps or faults the device.
  */
 Q4B_API int q4b_wait_status(void *stream, int *detail);

@@ -18,12 +18,16 @@ from .quantization import (  # noqa: E402
     dequantize_ggml_q4_0,
     dequantize_int4,
     matmul_ggml_q4_0,
+    fused_rmsnorm_linear_int4,
     matmul_int4,
+    matmul_int4_gelu,
+    matmul_int4_silu,
     matmul_int8,
     prepack_ggml_q4_0,
     prepack_int4,
     quantize_ggml_q4_0,
     quantize_int4,
+    rmsnorm,
     unpack_ggml_q4_0,
 )
 from .sharding import ColumnParallelQ4Linear, shard_bounds  # noqa: E402
@@ -40,7 +44,8 @@ def has_native_kernels() -> bool:
 
 __all__ = [
     "quantize_ggml_q4_0", "dequantize_ggml_q4_0", "matmul_ggml_q4_0", "prepack_ggml_q4_0",
-    "unpack_ggml_q4_0", "Q4Prepacked", "Int4Linear", "Q4Linear", "prepack_int4", "quantize_int4", "dequantize_int4", "matmul_int4",
+    "unpack_ggml_q4_0", "Q4Prepacked", "Int4Linear", "Q4Linear", "prepack_int4", "quantize_int4", "dequantize_int4", "matmul_int4", "matmul_int4_silu", "matmul_int4_gelu",
+    "fused_rmsnorm_linear_int4", "rmsnorm",
     "matmul_int8", "ColumnParallelQ4Linear", "shard_bounds", "has_native_kernels", "QK4_0",
     "BLOCK_Q4_0_SIZE",
 ]

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libq4b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
-FLAG_NONE, FLAG_PDL, FLAG_DECODE_TMEM, FLAG_GEMM_PAIR = 0, 1, 2, 4
+FLAG_NONE, FLAG_PDL, FLAG_DECODE_TMEM, FLAG_GEMM_PAIR, FLAG_ACT_SILU, FLAG_ACT_GELU = 0, 1, 2, 4, 8, 16
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_ARCH, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(9)
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
@@ -37,6 +37,7 @@ SYMBOLS = {
     "q4b_gemm": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
+    "q4b_rmsnorm": (_ci, [_vp, _ci, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp]),
     "q4b_matmul_host": (_ci, [_vp, _vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp, _ci, _vp]),
     "q4b_matmul_host_noalloc": (_ci, [_vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp]),
     "q4b_gemv_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _ci, _vp]),

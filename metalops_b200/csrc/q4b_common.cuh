@@ -131,6 +131,15 @@ __device__ __forceinline__ void dequant_word_biased(uint32_t w, uint32_t (&h)[4]
     }
 }
 
+// ---- epilogue activation (flags Q4B_FLAG_ACT_*: 0 none, 1 SiLU, 2 tanh-GELU), applied to the fp32 sum ----
+// Formulas of the reference's fused kernels (quant_kernels.metal:997, 1125-1131).
+__host__ __device__ inline int act_of_flags(int flags) { return (flags >> 3) & 3; }
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == 1) return v / (1.0f + __expf(-v));
+    if (act == 2) return v * 0.5f * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v;
+}
+
 // ---- host-side helpers ---------------------------------------------------------------
 void set_cuda_error(cudaError_t e);
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }

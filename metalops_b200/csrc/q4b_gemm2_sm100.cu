@@ -221,7 +221,7 @@ template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
                  uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int bn,
-                 const float *__restrict__ addend, int64_t ld_add) {
+                 const float *__restrict__ addend, int64_t ld_add, int act) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -391,6 +391,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
                     for (int j = 0; j < 32; ++j)
                         if (n0 + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + arow[j]);
                 }
+                if (act != 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(apply_act(__uint_as_float(r[j]), act));
+                }
                 if (m < M && n0 < N) {
                     if (vec_store && n0 + 32 <= N) {
 #pragma unroll
@@ -516,7 +520,7 @@ static EncodeTiledFn get_encode_fn() {
 
 template <bool BF16>
 static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M, int N, int K, int64_t ldy,
-                  int vec_store, int sms, const float *addend, int64_t ld_add, cudaStream_t st) {
+                  int vec_store, int sms, const float *addend, int64_t ld_add, int act, cudaStream_t st) {
     // Columns per pair tile: least (waves of CTA pairs x tile width), slightly biased to wide tiles
     const int mt = (M + PAIR_M - 1) / PAIR_M;
     const int pairs_max = sms / 2;
@@ -544,7 +548,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BF16>, tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K, ldy,
-                                    vec_store, bn, addend, ld_add));
+                                    vec_store, bn, addend, ld_add, act));
     return Q4B_OK;
 }
 
@@ -554,7 +558,7 @@ int device_sm_count();
 
 // Arguments as checked by q4b_gemm_addend.
 int gemm2_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int K, int N, const float *addend,
-                 int64_t ld_add, void *y, int64_t ldy, cudaStream_t st) {
+                 int64_t ld_add, void *y, int64_t ldy, int act, cudaStream_t st) {
     gemm2::EncodeTiledFn enc = gemm2::get_encode_fn();
     if (enc == nullptr) return Q4B_ERR_CUDA;
     CUtensorMap tmap;
@@ -568,8 +572,8 @@ int gemm2_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepac
     if (r != CUDA_SUCCESS) return Q4B_ERR_ARG;
     const int vec_store = (aligned(y, 16) && ldy % 8 == 0) ? 1 : 0;
     const int sms = device_sm_count();
-    return bf16 ? gemm2::launch<true>(tmap, prepacked, y, M, N, K, ldy, vec_store, sms, addend, ld_add, st)
-                : gemm2::launch<false>(tmap, prepacked, y, M, N, K, ldy, vec_store, sms, addend, ld_add, st);
+    return bf16 ? gemm2::launch<true>(tmap, prepacked, y, M, N, K, ldy, vec_store, sms, addend, ld_add, act, st)
+                : gemm2::launch<false>(tmap, prepacked, y, M, N, K, ldy, vec_store, sms, addend, ld_add, act, st);
 }
 
 int gemm2_wait_status(int *value) {

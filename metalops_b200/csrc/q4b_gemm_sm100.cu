@@ -218,7 +218,7 @@ template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
                     uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int bn,
-                    const float *__restrict__ addend, int64_t ld_add) {
+                    const float *__restrict__ addend, int64_t ld_add, int act) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -373,6 +373,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                         for (int j = 0; j < 32; ++j)
                             if (n0 + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + arow[j]);
                     }
+                    if (act != 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(apply_act(__uint_as_float(r[j]), act));
+                    }
                     if (m < M && n0 < N) {
                         if (vec_store && n0 + 32 <= N) {
 #pragma unroll
@@ -509,7 +513,7 @@ static EncodeTiledFn get_encode_fn() {
 
 template <bool BF16>
 static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M, int N, int K, int64_t ldy,
-                  int vec_store, int sms, const float *addend, int64_t ld_add, cudaStream_t st) {
+                  int vec_store, int sms, const float *addend, int64_t ld_add, int act, cudaStream_t st) {
     // Columns per tile: the candidate that needs the least (waves x tile width), with a small
     // bias towards wide tiles, whose MMAs and X loads are the more efficient.
     const int mt = (M + BM - 1) / BM;
@@ -526,7 +530,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
     const int tiles = mt * ((N + bn - 1) / bn);
     const int grid = tiles < sms ? tiles : sms;
     gemm_tcgen05_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K,
-                                                             ldy, vec_store, bn, addend, ld_add);
+                                                             ldy, vec_store, bn, addend, ld_add, act);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }
@@ -538,7 +542,7 @@ int gemv_wait_status(int *value);
 int gemv_tc_wait_status(int *value);
 int gemm2_wait_status(int *value);
 int gemm2_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int K, int N, const float *addend,
-                 int64_t ld_add, void *y, int64_t ldy, cudaStream_t st);
+                 int64_t ld_add, void *y, int64_t ldy, int act, cudaStream_t st);
 // Q4B_GEMM_PAIR=0/1 forces the CTA-pair prefill kernel off / on (benchmark sweeps only)
 static int gemm_pair_override() {
     static int v = -2;
@@ -570,7 +574,7 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     if (q4b_device_ok() != Q4B_OK) return Q4B_ERR_ARCH;
     if (gemm_pair_override() == 1 || ((flags & Q4B_FLAG_GEMM_PAIR) && gemm_pair_override() != 0 && M > gemm::HALF_M))
         return gemm2_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, (int)K, (int)N, addend, ld_add, y, ldy,
-                            (cudaStream_t)stream);
+                            act_of_flags(flags), (cudaStream_t)stream);
     gemm::EncodeTiledFn enc = gemm::get_encode_fn();
     if (enc == nullptr) return Q4B_ERR_CUDA;
 
@@ -588,8 +592,10 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     const int sms = device_sm_count();
     cudaStream_t st = (cudaStream_t)stream;
     return x_dtype == Q4B_BF16
-               ? gemm::launch<true>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, addend, ld_add, st)
-               : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, addend, ld_add, st);
+               ? gemm::launch<true>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, addend, ld_add,
+                                    act_of_flags(flags), st)
+               : gemm::launch<false>(tmap, prepacked, y, (int)M, (int)N, (int)K, ldy, vec_store, sms, addend, ld_add,
+                                     act_of_flags(flags), st);
 }
 
 #ifdef Q4B_GEMM_PROFILE

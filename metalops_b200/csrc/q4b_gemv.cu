@@ -223,7 +223,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
 template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *__restrict__ prepacked, int64_t K,
-            int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add) {
+            int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add, int act) {
     using G = SlotGeom<CHUNK>;
     constexpr int NTC = GEMV_WARPS / KS;
     extern __shared__ __align__(128) uint8_t ring_all[];
@@ -357,6 +357,7 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 #pragma unroll
             for (int j = 0; j < KS; ++j) s += red[tl * KS + j][f][m8 * TILE_N + nl];
             if (addend != nullptr) s += addend[(size_t)m * ld_add + n];     // fp32 term added before the one rounding
+            s = apply_act(s, act);
             y[(size_t)m * ldy + n] = out_bits<BF16>(s);
         }
     }
@@ -388,7 +389,7 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add));
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add, act_of_flags(flags)));
     return Q4B_OK;
 }
 
@@ -410,7 +411,7 @@ template <int CHUNK, int SLOTS> struct M1Geom {
 template <bool BF16, int KS, int CHUNK, int SLOTS>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepacked, int64_t K, int64_t N,
-               uint16_t *__restrict__ y, const float *__restrict__ addend) {
+               uint16_t *__restrict__ y, const float *__restrict__ addend, int act) {
     using G = M1Geom<CHUNK, SLOTS>;
     constexpr int NTC = GEMV_WARPS / KS;
     extern __shared__ __align__(128) uint8_t ring_all[];
@@ -571,7 +572,7 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
 #pragma unroll
             for (int j = 0; j < KS; ++j) sum += red[tl * KS + j][nl];
             if (addend != nullptr) sum += addend[n];           // fp32 term added before the one rounding
-            y[n] = out_bits<BF16>(sum);
+            y[n] = out_bits<BF16>(apply_act(sum, act));
         }
     }
 #ifdef Q4B_GEMV_TRACE
@@ -614,7 +615,7 @@ static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_m1_kernel<BF16, KS, CHUNK, SLOTS>, (const uint16_t *)x,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend));
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend, act_of_flags(flags)));
     return Q4B_OK;
 }
 

@@ -172,7 +172,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, int m, int n) {
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 2)
 gemv_tc_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepacked, int64_t K, int64_t N,
-               uint16_t *__restrict__ y, const float *__restrict__ addend, int KS) {
+               uint16_t *__restrict__ y, const float *__restrict__ addend, int KS, int act) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -419,6 +419,7 @@ done:
         const int n = nt0 * TILE_N + (int)threadIdx.x;
         if (n < N && !s_abort) {
             if (addend != nullptr) sum += addend[n];           // fp32 term added before the one rounding
+            sum = apply_act(sum, act);
             if constexpr (BF16) y[n] = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
             else y[n] = __half_as_ushort(__float2half_rn(sum));
         }
@@ -463,7 +464,7 @@ static int launch(const void *x, const void *prepacked, int64_t K, int64_t N, vo
     cfg.attrs = attr;
     cfg.numAttrs = (unsigned)na;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_tc_kernel<BF16>, (const uint16_t *)x, (const uint8_t *)prepacked, K, N,
-                                    (uint16_t *)y, addend, ks));
+                                    (uint16_t *)y, addend, ks, act_of_flags(flags)));
     return Q4B_OK;
 }
 

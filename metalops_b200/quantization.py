@@ -308,7 +308,11 @@ def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
     return out
 
 
-def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+_ACT_FLAGS = {None: 0, "none": 0, "silu": _cabi.FLAG_ACT_SILU, "gelu": _cabi.FLAG_ACT_GELU}
+
+
+def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None,
+                           activation: Optional[str] = None) -> torch.Tensor:
     in_dtype = X2.dtype
     x = X2.half() if in_dtype == torch.float32 else X2
     if x.dtype not in (torch.float16, torch.bfloat16):
@@ -325,12 +329,12 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
     _cabi.check(rc, "matmul_int4")
     if bias is not None:
         addend += bias.float()
-    y = _matmul_prepacked(x, pre.tiles, addend=addend)
+    y = _matmul_prepacked(x, pre.tiles, addend=addend, flags=_ACT_FLAGS[activation])
     return y.float() if in_dtype == torch.float32 else y
 
 
 def matmul_int4(X: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
-                group_size: int = 128) -> torch.Tensor:
+                group_size: int = 128, activation: Optional[str] = None) -> torch.Tensor:
     """``Y = X @ ((q - zero) * scale)`` for ``X [M, K]`` or ``[B, M, K]`` — quantization.py:156-239.
 
     Runs the fused kernels (decode GEMV for M <= 16, tcgen05 GEMM above) on a one-time
@@ -341,8 +345,50 @@ def matmul_int4(X: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor, z
     X2 = X.reshape(-1, X.shape[-1]) if batched else X
     if X2.dim() != 2:
         raise RuntimeError("X must be [M, K] or [B, M, K]")
-    Y = _matmul_int4_prepacked(X2, prepack_int4(W_packed, scales, zeros, group_size))
+    Y = _matmul_int4_prepacked(X2, prepack_int4(W_packed, scales, zeros, group_size), activation=activation)
     return Y.view(X.shape[0], X.shape[1], -1) if batched else Y
+
+
+def matmul_int4_silu(X, W_packed, scales, zeros, group_size: int = 128) -> torch.Tensor:
+    """``silu(X @ dequant(W))`` with the activation fused into the matmul's epilogue (applied to the
+    fp32 sum, one rounding) — the backend entry ``matmul_int4_silu`` of the reference
+    (core_mps.mm:5784-5850, kernel quant_kernels.metal:880-1010)."""
+    return matmul_int4(X, W_packed, scales, zeros, group_size, activation="silu")
+
+
+def matmul_int4_gelu(X, W_packed, scales, zeros, group_size: int = 128) -> torch.Tensor:
+    """``gelu(X @ dequant(W))``, tanh form, fused like :func:`matmul_int4_silu` — the reference's
+    ``matmul_int4_gelu`` (core_mps.mm:5853-5914, kernel quant_kernels.metal:1015-1144)."""
+    return matmul_int4(X, W_packed, scales, zeros, group_size, activation="gelu")
+
+
+def rmsnorm(X: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``X * rsqrt(mean(X^2, -1) + eps) * weight`` for fp16/bf16 ``X [M, K]``, sums in fp32, one
+    rounding to ``X.dtype`` — the RMSNorm step of the reference's ``fused_rmsnorm_linear_int4``
+    (training_kernels.metal:425-485)."""
+    _cabi.require_device(X, "X")
+    if X.dim() != 2 or X.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("X must be a float16 or bfloat16 [M, K] tensor")
+    x = X if X.stride(1) == 1 else X.contiguous()
+    w = weight.to(device=x.device, dtype=x.dtype).contiguous()
+    if w.numel() != x.shape[1]:
+        raise RuntimeError(f"weight has {w.numel()} elements, X has K = {x.shape[1]}")
+    y = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    if x.shape[0] == 0:
+        return y
+    with torch.cuda.device(x.device):
+        rc = _cabi.load().q4b_rmsnorm(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], x.shape[0], x.shape[1], x.stride(0),
+                                      w.data_ptr(), float(eps), y.data_ptr(), y.stride(0), _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "rmsnorm")
+    return y
+
+
+def fused_rmsnorm_linear_int4(X: torch.Tensor, W_norm: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor,
+                              zeros: torch.Tensor, eps: float, group_size: int) -> torch.Tensor:
+    """RMSNorm followed by the group-wise INT4 linear layer, the reference's backend entry of the same
+    name and argument order (core_mps.mm:3017-3103): like there, two kernels back to back on one
+    stream with the normalised activations rounded to ``X.dtype`` in between."""
+    return matmul_int4(rmsnorm(X, W_norm, eps), W_packed, scales, zeros, group_size)
 
 
 def matmul_int8(X, W_packed, scales, zeros, group_size: int = 128):

@@ -130,3 +130,72 @@ def test_int4_errors(mo, cuda_dev):
         mo.matmul_int4(torch.zeros(1, 64, device=cuda_dev, dtype=torch.float16), p, s, zz, 16)   # group % 32 != 0
     with pytest.raises(NotImplementedError):
         mo.matmul_int8(None, None, None, None)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 40, 300])
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_matmul_int4_fused_activation(mo, cuda_dev, M, act):
+    """matmul_int4_silu / matmul_int4_gelu: the activation is applied to the fp32 sum in the
+    kernels' epilogues (decode, prefill) — compared with activation(fp32 reference matmul)."""
+    g = torch.Generator().manual_seed(7000 + M)
+    K, N, gs = 512, 328, 128
+    w = torch.randn(K, N, generator=g) * 0.05
+    x = torch.randn(M, K, generator=g).half()
+    packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), gs)
+    wd = mo.dequantize_int4(packed, scales, zeros, gs, torch.float32).cpu()
+    lin = x.float() @ wd
+    ref = torch.nn.functional.silu(lin) if act == "silu" else torch.nn.functional.gelu(lin, approximate="tanh")
+    fn = mo.matmul_int4_silu if act == "silu" else mo.matmul_int4_gelu
+    y = fn(x.to(cuda_dev), packed, scales, zeros, gs)
+    assert y.dtype == x.dtype and tuple(y.shape) == (M, N)
+    assert orc.rel_l2(y, ref) <= TOL
+    # the unfused composition agrees too
+    y_lin = mo.matmul_int4(x.to(cuda_dev), packed, scales, zeros, gs).float().cpu()
+    y_unfused = torch.nn.functional.silu(y_lin) if act == "silu" else torch.nn.functional.gelu(y_lin, approximate="tanh")
+    assert orc.rel_l2(y, y_unfused) <= TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [1, 7, 33])
+def test_rmsnorm_and_fused_rmsnorm_linear_int4(mo, cuda_dev, M, dtype):
+    """rmsnorm against the fp32 formula with one rounding (bit-exact when the fp32 sums agree, so
+    compared by tolerance of one ulp-scale), and fused_rmsnorm_linear_int4 against the composition
+    the reference runs: rmsnorm rounded to X.dtype, then the INT4 matmul."""
+    g = torch.Generator().manual_seed(8000 + M)
+    K, N, gs, eps = 1024, 200, 128, 1e-5
+    x = (torch.randn(M, K, generator=g) * 1.5).to(dtype)
+    wn = (1.0 + 0.1 * torch.randn(K, generator=g)).to(dtype)
+    w = torch.randn(K, N, generator=g) * 0.05
+    xn = mo.rmsnorm(x.to(cuda_dev), wn.to(cuda_dev), eps)
+    assert xn.dtype == dtype and tuple(xn.shape) == (M, K)
+    xf = x.float()
+    ref_n = (xf * torch.rsqrt(xf.pow(2).mean(dim=1, keepdim=True) + eps) * wn.float())
+    assert orc.rel_l2(xn, ref_n) <= (2e-3 if dtype == torch.bfloat16 else 3e-4)      # one rounding to dtype
+    assert torch.equal(xn, mo.rmsnorm(x.to(cuda_dev), wn.to(cuda_dev), eps)), "two runs differ bitwise"
+    packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), gs)
+    y = mo.fused_rmsnorm_linear_int4(x.to(cuda_dev), wn.to(cuda_dev), packed, scales, zeros, eps, gs)
+    wd = mo.dequantize_int4(packed, scales, zeros, gs, torch.float32).cpu()
+    ref = xn.float().cpu() @ wd
+    assert y.dtype == dtype and tuple(y.shape) == (M, N)
+    assert orc.rel_l2(y, ref) <= TOL
+
+
+def test_activation_on_q4_0_kernels_all_paths(mo, cuda_dev):
+    """The activation flag on every matmul kernel: single-row and multi-row decode, the
+    tensor-memory decode kernel, the prefill kernel and its CTA-pair variant."""
+    from metalops_b200 import _cabi, quantization as Q
+    g = torch.Generator().manual_seed(9001)
+    K, N = 1024, 520
+    w = torch.randn(K, N, generator=g) * 0.05
+    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+    pre = mo.prepack_ggml_q4_0(blocks)
+    wd = mo.dequantize_ggml_q4_0(blocks, torch.float32).cpu()
+    for M, kernel, extra in ((1, "gemv", 0), (1, "gemv", _cabi.FLAG_DECODE_TMEM), (6, "gemv", 0), (14, "gemv", 0),
+                             (70, "gemm", 0), (400, "gemm", 0), (400, "gemm", _cabi.FLAG_GEMM_PAIR)):
+        x = torch.randn(M, K, generator=g).half()
+        lin = x.float() @ wd
+        for flag, ref in ((_cabi.FLAG_ACT_SILU, torch.nn.functional.silu(lin)),
+                          (_cabi.FLAG_ACT_GELU, torch.nn.functional.gelu(lin, approximate="tanh"))):
+            y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel=kernel, flags=flag | extra)
+            assert orc.rel_l2(y, ref) <= TOL, (M, kernel, extra, flag)
+    assert Q.wait_status(cuda_dev) == 0
