@@ -53,12 +53,12 @@ def recorded_traffic():
     """DRAM traffic figures taken from the committed ncu summaries (dram__bytes_read.sum +
     dram__bytes_write.sum of one captured launch; the bench never runs under a profiler).
 
-    gemv: profiles/gemv_kernel_llama7b_layer.md — DRAM bytes / algorithmic bytes measured on the
+    gemv: profiles/gemv_m1_kernel_llama7b_layer.md — DRAM bytes / algorithmic bytes measured on the
     three shapes of a layer (1.002, 1.000, 1.001), i.e. traffic grows in proportion to the bytes
     of a launch; the step's average launch is scaled by that ratio.
-    gemm: profiles/gemm_tcgen05_kernel_m2048.md — 50.0 MB read + 15.0 MB written for the bench's
+    gemm: profiles/gemm_tcgen05_kernel_m2048.md — 50.0 MB read + 12.1 MB written for the bench's
     M=2048, K=4096, N=14336 launch."""
-    return {"gemv_dram_bytes_per_algorithmic_byte": 1.001, "gemm_dram_bytes_per_launch": 65.0e6}
+    return {"gemv_dram_bytes_per_algorithmic_byte": 1.001, "gemm_dram_bytes_per_launch": 62.1e6}
 
 
 class ClockSampler:
