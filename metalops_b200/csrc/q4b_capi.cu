@@ -121,7 +121,10 @@ extern "C" int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, co
 extern "C" int q4b_matmul_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                                  int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
                                  void *stream) {
-    if (M >= 1 && M <= 16)
+    // Up to 8 rows: decode kernels.  9..16 rows: decode kernel for small weights, else the
+    // tensor-memory kernel behind q4b_gemm (measured crossover: the decode kernel re-reads x per
+    // column tile, which at 16 rows is 3.5x the weight bytes).  More rows: q4b_gemm.
+    if (M >= 1 && (M <= 8 || (M <= 16 && K * N < (1LL << 25))))
         return q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, stream);
     return q4b_gemm_addend(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, stream);
 }

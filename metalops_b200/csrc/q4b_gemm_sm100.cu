@@ -543,6 +543,18 @@ int gemv_tc_wait_status(int *value);
 int gemm2_wait_status(int *value);
 int gemm2_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int K, int N, const float *addend,
                  int64_t ld_add, void *y, int64_t ldy, int act, cudaStream_t st);
+int gemm_tmem_wait_status(int *value);
+int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                     const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
+// Q4B_GEMM_TMEM=0/1 forces the small-batch tensor-memory kernel off / on for M <= 128 (benchmark sweeps only)
+static int gemm_tmem_override() {
+    static int v = -2;
+    if (v == -2) {
+        const char *e = getenv("Q4B_GEMM_TMEM");
+        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
+    }
+    return v;
+}
 // Q4B_GEMM_PAIR=0/1 forces the CTA-pair prefill kernel off / on (benchmark sweeps only)
 static int gemm_pair_override() {
     static int v = -2;
@@ -572,6 +584,14 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
     if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
     if (q4b_device_ok() != Q4B_OK) return Q4B_ERR_ARCH;
+    // Up to 128 rows: the tensor-memory kernel (weights as the A operand), whose step cost does not
+    // depend on M, unless the weight has more 128-column panels than two per SM (it is not
+    // persistent: several waves of CTAs each pay its prologue and reduction).
+    int use_tmem = gemm_tmem_override();
+    if (use_tmem < 0) use_tmem = ceil_div(tiles_n(N), 8) <= 2 * device_sm_count() ? 1 : 0;
+    if (M <= 128 && use_tmem == 1)
+        return gemm_tmem_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags,
+                                (cudaStream_t)stream);
     if (gemm_pair_override() == 1 || ((flags & Q4B_FLAG_GEMM_PAIR) && gemm_pair_override() != 0 && M > gemm::HALF_M))
         return gemm2_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, (int)K, (int)N, addend, ld_add, y, ldy,
                             act_of_flags(flags), (cudaStream_t)stream);
@@ -617,6 +637,8 @@ extern "C" int q4b_wait_status(void *stream, int *detail) {
     if (int rc = gemv_tc_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (int rc = gemm2_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = gemm_tmem_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (detail) *detail = h;
     return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;

@@ -271,3 +271,26 @@ def test_prefill_cta_pair_kernel(mo, cuda_dev, M, K, N, xdtype):
     assert torch.equal(y, y2), "two runs differ bitwise"
     y_default = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm")
     assert orc.rel_l2(y, y_default.float().cpu()) <= TOL
+
+
+@pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N", [(17, 512, 128), (33, 96, 48), (64, 4096, 1000), (100, 1056, 200), (128, 2048, 4112),
+                                   (20, 4096, 4096), (128, 11008, 4096)])
+def test_small_batch_tensor_memory_kernel(mo, cuda_dev, M, K, N, xdtype):
+    """17..128 rows run on the tensor-memory kernel (weights as the tcgen05 A operand, k split over a
+    thread-block cluster): tolerance, bitwise repeatability, no bounded wait gave up.  Covers row
+    counts that are not multiples of 16, column tails, an odd number of 32-k blocks, cluster sizes
+    1..8 and agreement with the decode kernel on the first 16 rows."""
+    from metalops_b200 import quantization as Q
+    w, x = make_case(6000 + M + K + N, M, K, N, xdtype)
+    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+    pre = mo.prepack_ggml_q4_0(blocks)
+    y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm")
+    assert Q.wait_status(cuda_dev) == 0
+    ref = c_oracle.matmul_f32(x, blocks.cpu())
+    assert torch.isfinite(y).all()
+    assert orc.rel_l2(y, ref) <= TOL
+    y2 = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm")
+    assert torch.equal(y, y2), "two runs differ bitwise"
+    y16 = Q._matmul_prepacked(x[:16].to(cuda_dev), pre, kernel="gemv")
+    assert orc.rel_l2(y[:16], y16.float().cpu()) <= TOL
