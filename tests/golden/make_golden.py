@@ -56,7 +56,9 @@ def make_weight(seed: int, K: int, N: int, dtype: torch.dtype, std: float) -> to
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the reference checkout>")
+    root = sys.argv[1]
     ref = load_reference(root)
     torch.set_num_threads(1)
 
