@@ -25,7 +25,7 @@
 // that gives up records a code and all roles fall through to the common exit.
 #include <cstdlib>
 
-#include "q4b_common.cuh"
+#include "q4b_sm100_ptx.cuh"
 
 namespace q4b {
 namespace gemvtc {
@@ -51,7 +51,6 @@ constexpr int SMEM_PART = SMEM_S + (X_MAX_ELEMS / QK) * 4;           // 2 x 128 
 constexpr int SMEM_BAR = SMEM_PART + 2 * PANEL_N * 4;
 constexpr int NUM_BARS = 2 * NSTAGE + 2 * TM_STAGES + 1;
 constexpr int SMEM_DYN = SMEM_BAR + NUM_BARS * 8 + 128;
-constexpr long long WAIT_LIMIT_CYCLES = 1LL << 28;   // ~0.15 s; far above any legitimate wait
 
 __device__ int g_tc_status = 0;
 #ifdef Q4B_TC_PROFILE
@@ -64,92 +63,21 @@ __device__ unsigned long long g_tc_prof[16];
 #define PROF_ADD(slot)
 #endif
 
-// ---- thin PTX wrappers ---------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when another role aborted or when this wait ran out (it then records `code`,
-// first writer wins, and raises the CTA-wide abort flag).
+using namespace ptx;
+
+// bounded waits of this file record their code in g_tc_status
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    long long t0 = 0;
-    for (int it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63) == 0) {
-            if (*abort_flag) return false;
-            const long long now = clock64();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicCAS(&g_tc_status, 0, code);
-                return false;
-            }
-        }
-    }
+    return ptx::mbar_wait(bar, parity, abort_flag, &g_tc_status, code);
 }
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code));
+    return ptx::mbar_wait_warp(bar, parity, abort_flag, &g_tc_status, code);
 }
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-// true on one lane of the (converged) warp
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[tmem] . B[smem descriptor]
-__device__ __forceinline__ void tc_mma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                              uint32_t accumulate) {
-    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 16 registers -> 16 consecutive columns of the thread's own tensor-memory lane
-__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t tc_ld_32x32b_x1(uint32_t taddr) {
     uint32_t r;
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
     return r;
 }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void deq_group_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
 
 // K-major operand without swizzle: core matrices of 8 rows x 16 bytes.  Rows are 16 bytes apart
 // and the next core matrix along k starts 16 bytes on, so row 0 is 32 contiguous bytes of x and
@@ -161,12 +89,6 @@ __device__ __forceinline__ uint64_t make_x_desc(uint32_t smem_addr) {
     d |= (uint64_t)(128 >> 4) << 32;                 // stride byte offset: next 8 rows
     d |= (uint64_t)1 << 46;                          // descriptor version for sm_100
     return d;                                        // layout type 0: no swizzle
-}
-__host__ __device__ constexpr uint32_t make_idesc(bool bf16, int m, int n) {
-    return (1u << 4)                              // D format f32
-           | ((bf16 ? 1u : 0u) << 7)              // A format
-           | ((bf16 ? 1u : 0u) << 10)             // B format
-           | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 template <bool BF16>
