@@ -306,8 +306,11 @@ def run_ours(args) -> None:
 
     # ---- prefill GEMM (rank 0's GPU only at N > 1: the same kernel runs on every rank) -----
     gemm = None
+    batch = None
     if not args.skip_gemm:
         gemm = bench_gemm(dev, stream, lib, peaks, traffic, args)
+        if rank == 0 and args.layers >= 4:
+            batch = bench_batch(dev, stream, lib, stack, flags)
 
     out = None
     if rank == 0:
@@ -333,6 +336,8 @@ def run_ours(args) -> None:
         }
         if gemm is not None:
             out["gemm"] = gemm
+        if batch is not None:
+            out["decode_batch"] = batch
     if rank == 0 and not args.skip_cpu and world >= 1:
         out["cpu_baseline"] = cpu_baseline()
     if rank == 0:
@@ -405,6 +410,48 @@ def bench_gemm(dev, stream, lib, peaks, traffic, args):
                          "frac_of_nominal_2250": tf / 2250.0, "peak_source": peaks["source"],
                          "kernel": "gemm_tcgen05_kernel", "traffic": traffic.get("gemm_dram_bytes_per_launch")},
             "gpu_launches": reps}
+
+
+def bench_batch(dev, stream, lib, stack, flags):
+    """Decode batches: the same projections at M = 4, 16 and 64 rows through q4b_matmul (decode kernel,
+    tensor-memory kernel), the first four layers (455 MB of weights, larger than L2) in a CUDA
+    graph.  Reported for information next to the M = 1 headline."""
+    from metalops_b200 import _cabi
+    sub = stack[: 4 * len(PROJ)]
+    out = {}
+    for M in (4, 16, 64):
+        xs = {K: torch.randn(M, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
+        ys = [torch.empty(M, N, device=dev, dtype=torch.float16) for _, _, N, _ in sub]
+
+        def enqueue():
+            sp = torch.cuda.current_stream(dev).cuda_stream
+            for (name, K, N, pre), y in zip(sub, ys):
+                rc = lib.q4b_matmul(xs[K].data_ptr(), _cabi.F16, M, K, pre.data.data_ptr(), K, N, y.data_ptr(), N, flags, sp)
+                if rc:
+                    _cabi.check(rc, "q4b_matmul")
+
+        with torch.cuda.stream(stream):
+            enqueue()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                enqueue()
+            for _ in range(3):
+                g.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 20
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        nbytes = sum(gemv_bytes(M, K, N) for _, K, N, _ in sub)
+        flops = sum(2.0 * M * K * N for _, K, N, _ in sub)
+        out[f"m{M}"] = {"gbps": nbytes / (ms * 1e-3) / 1e9, "tflops": flops / (ms * 1e-3) / 1e12,
+                        "us_per_launch": ms * 1e3 / len(sub)}
+    return out
 
 
 def main() -> None:
