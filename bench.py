@@ -454,6 +454,30 @@ def bench_batch(dev, stream, lib, stack, flags):
     return out
 
 
+def run_probe(spec: str) -> None:
+    """`--probe MxKxN`: six distinct weights, one q4b_matmul launch each (fp16 activations), then the
+    wait status; prints the average device time.  A small fixed case for profiler captures."""
+    from metalops_b200 import _cabi
+    from metalops_b200 import quantization as Q
+    M, K, N = (int(v) for v in spec.lower().split("x"))
+    dev = torch.device("cuda", 0)
+    lib = _cabi.load()
+    g = torch.Generator(device=dev).manual_seed(4242)
+    pres = [Q._quantize_impl(torch.randn(K, N, generator=g, device=dev) * 0.02, False, True)[1] for _ in range(6)]
+    x = torch.randn(M, K, generator=g, device=dev).half()
+    y = torch.empty(M, N, device=dev, dtype=torch.float16)
+    sp = _cabi.stream_ptr(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for p in pres:
+        _cabi.check(lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, p.data.data_ptr(), K, N, y.data_ptr(), N, 0, sp), "q4b_matmul")
+    e1.record()
+    torch.cuda.synchronize(dev)
+    print(json.dumps({"probe": spec, "launches": len(pres), "us_per_launch": e0.elapsed_time(e1) * 1e3 / len(pres),
+                      "wait_status": Q.wait_status(dev)}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -464,10 +488,14 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--probe", default=None, metavar="MxKxN", help="run one small product six times and exit (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-gemm", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
+    if args.probe:
+        run_probe(args.probe)
+        return
     if args.impl == "reference":
         if args.steps > 20:
             args.steps = 20
