@@ -186,6 +186,18 @@ Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
                              int64_t K, int64_t N, int64_t group, float *addend_out, void *stream);
 
 /*
+ * Decode product with a fused all-gather (column-parallel layers over several GPUs of one box; no
+ * reference counterpart, the reference is single-device): q4b_gemv, but each rank's kernel stores
+ * its [M, N] result at column offset col0 of the [M, ld_out] output of EVERY rank, through
+ * peer-mapped device pointers y_ranks[0..world-1] (a HOST array; plain stores over NVLink), instead
+ * of into a local y.  The caller provides the peer mapping (e.g. torch symmetric memory) and the
+ * barrier after which the gathered outputs may be read.  1 <= M <= 16, world <= 8.
+ */
+Q4B_API int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ldx,
+                            const void *prepacked, int64_t K, int64_t N, void *const *y_ranks,
+                            int world, int64_t col0, int64_t ld_out, int flags, void *stream);
+
+/*
  * RMSNorm in front of a quantised linear layer, the first step of the reference's
  * fused_rmsnorm_linear_int4 (core_mps.mm:3017-3103; kernel training_kernels.metal:425-485):
  * y[m, :] = T(float(x[m, :]) * rsqrt(mean(x[m, :]^2) + eps) * float(weight[:])), sums in fp32.

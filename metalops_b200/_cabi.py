@@ -37,6 +37,7 @@ SYMBOLS = {
     "q4b_gemm": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
+    "q4b_gemv_gather": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _vp]),
     "q4b_rmsnorm": (_ci, [_vp, _ci, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp]),
     "q4b_matmul_host": (_ci, [_vp, _vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp, _ci, _vp]),
     "q4b_matmul_host_noalloc": (_ci, [_vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp]),

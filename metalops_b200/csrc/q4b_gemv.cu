@@ -31,6 +31,16 @@ constexpr int GEMV_SPIN_LIMIT = 1 << 22;            // try_wait polls before giv
 
 __device__ int g_wait_status = 0;                  // first bounded wait of this file that gave up
 
+// Optional fused all-gather: when `world` > 0 the epilogue stores the result, instead of into y, at
+// column offset col0 of the [M, ld]-shaped output of EVERY rank (peer-mapped pointers; plain
+// stores over NVLink), so the column-parallel shards land gathered without a collective.
+struct PeerOut {
+    uint16_t *p[8];
+    int world;
+    int64_t col0, ld;
+};
+static thread_local PeerOut tl_peers = {};          // set by q4b_gemv_gather around the dispatch
+
 #ifdef Q4B_GEMV_TRACE
 // development aid: one record per CTA (weights pointer, block | sm << 32, four global-timer stamps)
 constexpr int TRACE_MAX = 1 << 16;
@@ -220,10 +230,11 @@ template <bool BF16> __device__ __forceinline__ uint16_t out_bits(float v) {
 
 // KS = warps of a CTA that split k for the same column tile; the CTA covers 8/KS column tiles.
 // CHUNK tiles per ring slot, SLOTS slots per warp.
-template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS, bool GATHER>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *__restrict__ prepacked, int64_t K,
-            int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add, int act) {
+            int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add, int act,
+            const PeerOut peers) {
     using G = SlotGeom<CHUNK>;
     constexpr int NTC = GEMV_WARPS / KS;
     extern __shared__ __align__(128) uint8_t ring_all[];
@@ -358,14 +369,21 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
             for (int j = 0; j < KS; ++j) s += red[tl * KS + j][f][m8 * TILE_N + nl];
             if (addend != nullptr) s += addend[(size_t)m * ld_add + n];     // fp32 term added before the one rounding
             s = apply_act(s, act);
-            y[(size_t)m * ldy + n] = out_bits<BF16>(s);
+            const uint16_t bits = out_bits<BF16>(s);
+            if constexpr (!GATHER) {
+                y[(size_t)m * ldy + n] = bits;
+            } else {
+#pragma unroll
+                for (int r = 0; r < 8; ++r)        // static indices: the pointers stay in the parameter bank
+                    if (r < peers.world) peers.p[r][(size_t)m * peers.ld + peers.col0 + n] = bits;
+            }
         }
     }
 }
 
-template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
-static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
-                       int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS, bool GATHER>
+static int launch_gemv_impl(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
+                            int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
     constexpr int NTC = GEMV_WARPS / KS;
     const int smem = GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(M);
     // opt in to > 48 KB of dynamic shared memory once per device and instantiation
@@ -373,7 +391,7 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>,
+        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS, CHUNK, SLOTS, GATHER>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(MF * 8)));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
@@ -388,9 +406,17 @@ static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
-    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS>, (const uint16_t *)x, M, ldx,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add, act_of_flags(flags)));
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS, GATHER>, (const uint16_t *)x, M, ldx,
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add, act_of_flags(flags), tl_peers));
     return Q4B_OK;
+}
+// the fused all-gather is its own instantiation, so that the plain kernel carries none of it
+template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
+static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
+                       int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
+    return tl_peers.world != 0
+               ? launch_gemv_impl<BF16, MF, KS, CHUNK, SLOTS, true>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st)
+               : launch_gemv_impl<BF16, MF, KS, CHUNK, SLOTS, false>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
 }
 
 // ---- single activation row ---------------------------------------------------------------
@@ -408,10 +434,10 @@ template <int CHUNK, int SLOTS> struct M1Geom {
     static constexpr int ZERO_BYTES = (SLOTS - 1) * SLOT_BYTES + X_BYTES;
 };
 
-template <bool BF16, int KS, int CHUNK, int SLOTS>
+template <bool BF16, int KS, int CHUNK, int SLOTS, bool GATHER>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepacked, int64_t K, int64_t N,
-               uint16_t *__restrict__ y, const float *__restrict__ addend, int act) {
+               uint16_t *__restrict__ y, const float *__restrict__ addend, int act, const PeerOut peers) {
     using G = M1Geom<CHUNK, SLOTS>;
     constexpr int NTC = GEMV_WARPS / KS;
     extern __shared__ __align__(128) uint8_t ring_all[];
@@ -572,7 +598,14 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
 #pragma unroll
             for (int j = 0; j < KS; ++j) sum += red[tl * KS + j][nl];
             if (addend != nullptr) sum += addend[n];           // fp32 term added before the one rounding
-            y[n] = out_bits<BF16>(apply_act(sum, act));
+            const uint16_t bits = out_bits<BF16>(apply_act(sum, act));
+            if constexpr (!GATHER) {
+                y[n] = bits;
+            } else {
+#pragma unroll
+                for (int r = 0; r < 8; ++r)        // static indices: the pointers stay in the parameter bank
+                    if (r < peers.world) peers.p[r][peers.col0 + n] = bits;
+            }
         }
     }
 #ifdef Q4B_GEMV_TRACE
@@ -590,9 +623,9 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
 #endif
 }
 
-template <bool BF16, int KS, int CHUNK, int SLOTS>
-static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend,
-                          int flags, cudaStream_t st) {
+template <bool BF16, int KS, int CHUNK, int SLOTS, bool GATHER>
+static int launch_gemv_m1_impl(const void *x, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend,
+                               int flags, cudaStream_t st) {
     using G = M1Geom<CHUNK, SLOTS>;
     constexpr int NTC = GEMV_WARPS / KS;
     // opt in to > 48 KB of dynamic shared memory once per device and instantiation
@@ -600,7 +633,7 @@ static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_m1_kernel<BF16, KS, CHUNK, SLOTS>,
+        Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_m1_kernel<BF16, KS, CHUNK, SLOTS, GATHER>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, G::RING_BYTES));
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -614,9 +647,15 @@ static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
-    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_m1_kernel<BF16, KS, CHUNK, SLOTS>, (const uint16_t *)x,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend, act_of_flags(flags)));
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_m1_kernel<BF16, KS, CHUNK, SLOTS, GATHER>, (const uint16_t *)x,
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend, act_of_flags(flags), tl_peers));
     return Q4B_OK;
+}
+template <bool BF16, int KS, int CHUNK, int SLOTS>
+static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend,
+                          int flags, cudaStream_t st) {
+    return tl_peers.world != 0 ? launch_gemv_m1_impl<BF16, KS, CHUNK, SLOTS, true>(x, prepacked, K, N, y, addend, flags, st)
+                               : launch_gemv_m1_impl<BF16, KS, CHUNK, SLOTS, false>(x, prepacked, K, N, y, addend, flags, st);
 }
 
 // Ring geometry by row count: shared memory per CTA = 8 warps x SLOTS x (CHUNK x 576 + M x row).
@@ -743,10 +782,28 @@ extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     if (ks == 0) ks = M == 1 ? m1_ksplit(NT, device_sm_count()) : 8;     // several rows: always 8 (measured)
     while (ks > 1 && KU < ks) ks /= 2;
     cudaStream_t st = (cudaStream_t)stream;
-    if (M == 1 && (gemv_tc_override() == 1 || ((flags & Q4B_FLAG_DECODE_TMEM) && gemv_tc_override() != 0))) {
+    if (M == 1 && tl_peers.world == 0 && (gemv_tc_override() == 1 || ((flags & Q4B_FLAG_DECODE_TMEM) && gemv_tc_override() != 0))) {
         const int tks = gemv_tc_ksplit(K, N, device_sm_count());
         if (tks > 0) return gemv_tc_launch(x, x_dtype == Q4B_BF16, prepacked, K, N, y, addend, tks, flags, st);
     }
     return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st)
                                : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+}
+
+extern "C" int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                               int64_t N, void *const *y_ranks, int world, int64_t col0, int64_t ld_out, int flags,
+                               void *stream) {
+    if (y_ranks == nullptr || world < 1 || world > 8 || col0 < 0 || ld_out < col0 + N) return Q4B_ERR_ARG;
+    for (int r = 0; r < world; ++r)
+        if (y_ranks[r] == nullptr || !aligned(y_ranks[r], 2)) return Q4B_ERR_ARG;
+    PeerOut po = {};
+    for (int r = 0; r < world; ++r) po.p[r] = (uint16_t *)y_ranks[r];
+    po.world = world;
+    po.col0 = col0;
+    po.ld = ld_out;
+    tl_peers = po;
+    // y itself is not written in this mode; the first rank pointer stands in for the argument checks
+    const int rc = q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y_ranks[0], ld_out, flags & ~Q4B_FLAG_DECODE_TMEM, stream);
+    tl_peers = PeerOut{};
+    return rc;
 }

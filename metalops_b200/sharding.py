@@ -78,3 +78,39 @@ class ColumnParallelQ4Linear(nn.Module):
     def forward(self, x: torch.Tensor, gather_output: bool = False) -> torch.Tensor:
         y = self._matmul(x, self.weight_blocks)
         return gather_columns(y, self.group, self.world) if gather_output else y
+
+    # ---- fused all-gather for decode (M <= 16): the kernel's epilogue stores into every rank's output ----
+    def enable_fused_gather(self, max_rows: int = 16, dtype: torch.dtype = torch.float16) -> None:
+        """Allocate the gathered output ``[max_rows, N]`` in symmetric memory (peer-mapped on every
+        rank of the group) once.  Needs equal shards (N divisible by the world size) and CUDA."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        if self.N % self.world:
+            raise RuntimeError("fused gather needs N divisible by the number of ranks")
+        dev = self.weight_blocks.device
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._gather_buf = symm_mem.empty((max_rows, self.N), dtype=dtype, device=dev)
+        self._gather_hdl = symm_mem.rendezvous(self._gather_buf, group)
+        self._gather_ptrs = [int(p) for p in self._gather_hdl.buffer_ptrs]
+
+    def forward_fused_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """``[M, N]`` on every rank, M <= 16: each rank's decode kernel writes its columns into all
+        ranks' outputs over NVLink; a symmetric-memory barrier on the stream orders the reads.  The
+        returned tensor is a view of the shared buffer, valid until the next call."""
+        import ctypes
+        from . import _cabi
+        if getattr(self, "_gather_hdl", None) is None:
+            raise RuntimeError("call enable_fused_gather() first")
+        M = x.shape[0]
+        if M > self._gather_buf.shape[0] or M > 16 or x.dtype != self._gather_buf.dtype:
+            raise RuntimeError("fused gather serves up to 16 rows of the dtype it was enabled for")
+        pre = Q.prepack_ggml_q4_0(self.weight_blocks)
+        xc = x.contiguous()
+        self._gather_hdl.barrier()                      # nobody still reads the previous result
+        ptrs = (ctypes.c_void_p * self.world)(*self._gather_ptrs)
+        with torch.cuda.device(xc.device):
+            rc = _cabi.load().q4b_gemv_gather(xc.data_ptr(), _cabi.DTYPE_CODE[xc.dtype], M, xc.stride(0), pre.data.data_ptr(),
+                                              pre.K, pre.N, ptrs, self.world, self.n0, self.N, 0, _cabi.stream_ptr(xc.device))
+        _cabi.check(rc, "q4b_gemv_gather")
+        self._gather_hdl.barrier()                      # every rank's stores have landed
+        return self._gather_buf[:M]
