@@ -1,4 +1,4 @@
-"""Column-parallel sharding of a q4_0 linear layer over the GPUs of one node.
+"""Column-parallel (and row-parallel) sharding of a q4_0 linear layer over the GPUs of one node.
 
 The reference is single-device; this is the multi-GPU form its q4_0 matmul takes here.  Every
 (k-block, n) quantization block is independent, so rank r of g owns the output columns
@@ -114,3 +114,82 @@ class ColumnParallelQ4Linear(nn.Module):
         _cabi.check(rc, "q4b_gemv_gather")
         self._gather_hdl.barrier()                      # every rank's stores have landed
         return self._gather_buf[:M]
+
+
+class RowParallelQ4Linear(nn.Module):
+    """One rank's slice of a q4_0 linear layer, row-parallel over K (the down-projection that
+    follows a column-parallel gate/up pair, whose sharded output it consumes as is).
+
+    Quantization blocks are 32 consecutive k of one column, so rank r of g owns the k range
+    ``[r*K/g, (r+1)*K/g)`` (a multiple of 64, one streaming tile) and the bits of its blocks are
+    those of the full weight.  ``forward(x)`` takes either the full ``[M, K]`` activations or this
+    rank's ``[M, K/g]`` slice, computes the partial product and sums the partials over the ranks:
+    one NCCL all-reduce (in fp32), or for decode (M <= 16) the fused form in which every rank's
+    kernel stores its partial into a slot of every rank's buffer and the sum is local.
+    """
+
+    def __init__(self, K: int, N: int, rank: int, world: int, group=None,
+                 matmul: Optional[Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = None):
+        super().__init__()
+        self.K, self.N, self.rank, self.world, self.group = K, N, rank, world, group
+        self.k0, self.k1 = shard_bounds(K, world, rank, multiple=64)
+        self._matmul = matmul or Q.matmul_ggml_q4_0
+        self.register_buffer("weight_blocks", torch.zeros(((self.k1 - self.k0) // Q.QK4_0, N, Q.BLOCK_Q4_0_SIZE),
+                                                          dtype=torch.uint8))
+
+    @classmethod
+    def from_float(cls, weight_kn: torch.Tensor, rank: int, world: int, group=None, matmul=None,
+                   quantize: Optional[Callable[[torch.Tensor], torch.Tensor]] = None) -> "RowParallelQ4Linear":
+        K, N = weight_kn.shape
+        mod = cls(K, N, rank, world, group=group, matmul=matmul)
+        mod.weight_blocks = (quantize or Q.quantize_ggml_q4_0)(weight_kn[mod.k0:mod.k1].contiguous())
+        return mod
+
+    def _local_x(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[1] == self.K:
+            return x[:, self.k0:self.k1]
+        if x.shape[1] != self.k1 - self.k0:
+            raise RuntimeError(f"x has {x.shape[1]} columns; expected {self.K} or this rank's {self.k1 - self.k0}")
+        return x
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        part = self._matmul(self._local_x(x).contiguous(), self.weight_blocks)
+        if self.world == 1:
+            return part
+        acc = part.float()
+        dist.all_reduce(acc, group=self.group)
+        return acc.to(part.dtype)
+
+    # ---- fused reduction for decode (M <= 16) ----
+    def enable_fused_reduce(self, max_rows: int = 16, dtype: torch.dtype = torch.float16) -> None:
+        """Allocate ``[max_rows, world * N]`` in symmetric memory: slot r of every rank's buffer
+        receives rank r's partial product."""
+        import torch.distributed._symmetric_memory as symm_mem
+        dev = self.weight_blocks.device
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._red_buf = symm_mem.empty((max_rows, self.world * self.N), dtype=dtype, device=dev)
+        self._red_hdl = symm_mem.rendezvous(self._red_buf, group)
+        self._red_ptrs = [int(p) for p in self._red_hdl.buffer_ptrs]
+
+    def forward_fused_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """``[M, N]`` on every rank, M <= 16: the decode kernel of each rank writes its partial
+        product into slot ``rank`` of all ranks' buffers over NVLink (q4b_gemv_gather); after a
+        symmetric-memory barrier every rank adds the slots in rank order, in fp32."""
+        import ctypes
+        from . import _cabi
+        if getattr(self, "_red_hdl", None) is None:
+            raise RuntimeError("call enable_fused_reduce() first")
+        xl = self._local_x(x).contiguous()
+        M = xl.shape[0]
+        if M > self._red_buf.shape[0] or M > 16 or xl.dtype != self._red_buf.dtype:
+            raise RuntimeError("fused reduce serves up to 16 rows of the dtype it was enabled for")
+        pre = Q.prepack_ggml_q4_0(self.weight_blocks)
+        self._red_hdl.barrier()                         # nobody still reads the previous partials
+        ptrs = (ctypes.c_void_p * self.world)(*self._red_ptrs)
+        with torch.cuda.device(xl.device):
+            rc = _cabi.load().q4b_gemv_gather(xl.data_ptr(), _cabi.DTYPE_CODE[xl.dtype], M, xl.stride(0), pre.data.data_ptr(),
+                                              pre.K, pre.N, ptrs, self.world, self.rank * self.N, self.world * self.N, 0,
+                                              _cabi.stream_ptr(xl.device))
+        _cabi.check(rc, "q4b_gemv_gather")
+        self._red_hdl.barrier()                         # every rank's partial has landed
+        return self._red_buf[:M].view(M, self.world, self.N).float().sum(dim=1).to(xl.dtype)

@@ -45,6 +45,17 @@ def _worker(rank: int, world: int, port: int, ret):
                                                                                fused_layer._gather_ptrs)
                 y_fused = layer.forward_fused_gather(x)
                 ok &= bool(torch.equal(y_fused, y_full))
+        # row-parallel (k-sharded) layer: NCCL all-reduce and the fused reduction against one GPU
+        K2, N2 = 2048, 1000
+        w2 = (torch.randn(K2, N2, generator=g) * 0.02).to(dev)
+        row = mo.RowParallelQ4Linear.from_float(w2, rank, world)
+        row.enable_fused_reduce(max_rows=16, dtype=torch.float16)
+        for M in (1, 7):
+            x2 = torch.randn(M, K2, generator=g).half().to(dev)
+            ref2 = mo.matmul_ggml_q4_0(x2, mo.quantize_ggml_q4_0(w2)).float()
+            for y2 in (row(x2), row.forward_fused_reduce(x2)):
+                ok &= tuple(y2.shape) == (M, N2)
+                ok &= bool(((y2.float() - ref2).norm() / ref2.norm()).item() <= 2e-3)
         torch.cuda.synchronize()
         ret[rank] = bool(ok)
     finally:

@@ -59,3 +59,39 @@ def test_column_parallel_gather_world2(M):
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, M, ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def _row_worker(rank: int, world: int, port: int, M: int, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from metalops_b200.sharding import RowParallelQ4Linear
+        g = torch.Generator().manual_seed(5)
+        K, N = 256, 48
+        w = torch.randn(K, N, generator=g) * 0.02
+        x = torch.randn(M, K, generator=g)
+        layer = RowParallelQ4Linear.from_float(
+            w, rank, world, quantize=orc.quantize_q4_0,
+            matmul=lambda xx, blocks: orc.matmul_q4_0_fp32(xx, blocks))
+        full_blocks = orc.quantize_q4_0(w)
+        # blocks are 32 consecutive k of a column: a k shard's blocks are the full weight's
+        ok = torch.equal(layer.weight_blocks, full_blocks[layer.k0 // 32:layer.k1 // 32])
+        y = layer(x)                                    # full activations: the layer slices them
+        y2 = layer(x[:, layer.k0:layer.k1])             # or this rank's slice
+        expect = orc.matmul_q4_0_fp32(x, full_blocks)
+        ok = ok and torch.equal(y, y2) and tuple(y.shape) == (M, N)
+        ok = ok and bool(((y - expect).norm() / expect.norm()).item() < 1e-5)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("M", [1, 5])
+def test_row_parallel_allreduce_world2(M):
+    world = 2
+    port = 30100 + (os.getpid() % 500) + M
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_row_worker, args=(world, port, M, ret), nprocs=world, join=True)
+    assert dict(ret) == {0: True, 1: True}
