@@ -199,23 +199,7 @@ struct RingPos {
     }
 };
 
-#ifndef Q4B_GEMM2_NACC
-#define Q4B_GEMM2_NACC 2
-#endif
-constexpr int NACC = Q4B_GEMM2_NACC;                 // accumulator buffers in tensor memory
-#ifdef Q4B_GEMM2_DEBUG
-__device__ unsigned int g_gemm2_dbg[8];              // development aid: TMEM base of the first two pairs' CTAs
-__device__ unsigned long long g_gemm2_prof[32];      // cycle counters of pair 0: [rank * 16 + slot]
-#define PROF_T0() const long long _pt = clock64()
-#define PROF_ADD(slot) prof[slot] += clock64() - _pt
-#define PROF_DECL() long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PROF_FLUSH(first, n) if (lane == 0 && blockIdx.x < 2) { for (int _j = 0; _j < (n); ++_j) g_gemm2_prof[rank * 16 + (first) + _j] = (unsigned long long)prof[_j]; }
-#else
-#define PROF_T0()
-#define PROF_ADD(slot)
-#define PROF_DECL()
-#define PROF_FLUSH(first, n)
-#endif
+constexpr int NACC = 2;                              // accumulator buffers in tensor memory
 
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -260,9 +244,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
     cluster_sync_all();                                // both CTAs' barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
-#ifdef Q4B_GEMM2_DEBUG
-    if (threadIdx.x == 0 && blockIdx.x < 4) { g_gemm2_dbg[blockIdx.x * 2] = tmem_base; g_gemm2_dbg[blockIdx.x * 2 + 1] = rank; }
-#endif
 
     const int NT = (int)tiles_n(N);
     const int w_tiles = bn / TILE_N, half_tiles = w_tiles / 2;     // column tiles of the pair / of this CTA
@@ -277,22 +258,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
         // ---------------- X producer ----------------
         if (lane == 0) {
             RingPos a;
-            PROF_DECL();
             for (int t = pair; t < num_tiles; t += num_pairs) {
                 const int mt = t % num_mt;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    { PROF_T0(); if (!mbar_wait(bar_empty_a(a.s), a.phase ^ 1, abort_flag, 301)) goto done; PROF_ADD(0); }
-#ifdef Q4B_GEMM2_NOX
-                    if (rank == 0) mbar_arrive(bar_full_a(a.s));
-#else
+                    if (!mbar_wait(bar_empty_a(a.s), a.phase ^ 1, abort_flag, 301)) goto done;
                     if (rank == 0) mbar_arrive_expect_tx(bar_full_a(a.s), 2u * A_BYTES);     // both CTAs' bytes
                     tma_load_2d_pair(base + SMEM_A + a.s * A_BYTES, &tmap_x, ks * BK, mt * PAIR_M + (int)rank * CTA_M,
                                      map_to_rank(bar_full_a(a.s), 0));
-#endif
                     a.advance(SA);
                 }
             }
-            PROF_FLUSH(0, 1);
         }
     } else if (warp == WARP_W) {
         // ---------------- packed-weight producer: lane i copies this CTA's column tile i of the step ----------------
@@ -320,19 +295,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
             const uint32_t idesc = make_idesc(BF16, PAIR_M, bn);
             RingPos a, b;
             int it = 0;
-            PROF_DECL();
-#ifdef Q4B_GEMM2_DEBUG
-            const long long prof_start = clock64();
-#endif
             for (int t = pair; t < num_tiles; t += num_pairs, ++it) {
                 const int ab = it % NACC;
-                { PROF_T0(); if (!mbar_wait_warp(bar_tempty(ab), (((uint32_t)(it / NACC)) & 1u) ^ 1u, abort_flag, 302)) goto done; PROF_ADD(0); }
+                if (!mbar_wait_warp(bar_tempty(ab), (((uint32_t)(it / NACC)) & 1u) ^ 1u, abort_flag, 302)) goto done;
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    { PROF_T0(); if (!mbar_wait_warp(bar_full_a(a.s), a.phase, abort_flag, 303)) goto done; PROF_ADD(1); }
-                    { PROF_T0(); if (!mbar_wait_warp(bar_full_b(b.s), b.phase, abort_flag, 304)) goto done; PROF_ADD(2); }
+                    if (!mbar_wait_warp(bar_full_a(a.s), a.phase, abort_flag, 303)) goto done;
+                    if (!mbar_wait_warp(bar_full_b(b.s), b.phase, abort_flag, 304)) goto done;
                     tc_fence_after();
-                    PROF_T0();
                     if (elect_one()) {
                         const uint64_t adesc = make_kmajor_sw128_desc(base + SMEM_A + a.s * A_BYTES);
                         const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + b.s * B_BYTES);
@@ -344,15 +314,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
                         if (ks == k_steps - 1) tc_commit_pair(bar_tfull(ab));
                     }
                     __syncwarp();
-                    PROF_ADD(3);
                     a.advance(SA);
                     b.advance(SB);
                 }
             }
-#ifdef Q4B_GEMM2_DEBUG
-            prof[4] = clock64() - prof_start;
-#endif
-            PROF_FLUSH(1, 5);
         } else if (lane == 0) {
             // Second CTA: relay.  Its dequantising warps arrive on their own CTA's "B full" barrier, which
             // is cheap; this otherwise idle thread passes each completed phase on to the first CTA, so the
@@ -429,7 +394,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
         const uint32_t qoff = (uint32_t)(dw * TILE_BYTES + slot_of(g, c) * 16);
         const uint32_t doff = (uint32_t)(dw * TILE_BYTES + TILE_QS_BYTES + g * 8);
         uint32_t step = 0;                               // running index over all (tile, k step) pairs of this CTA
-        PROF_DECL();
         for (int t = pair; t < num_tiles; t += num_pairs) {
             const int nt0 = (t / num_mt) * w_tiles + (int)rank * half_tiles;
             const int valid = max(0, min(half_tiles, NT - nt0));
@@ -437,12 +401,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
                 if ((int)(step % DEQ_GROUPS) != dgrp) continue;
                 const int ws = (int)(step % (uint32_t)sw), bs = (int)(step % SB);
                 const uint32_t wphase = (step / (uint32_t)sw) & 1u, bphase = (step / SB) & 1u;
-                { PROF_T0(); if (!mbar_wait_warp(bar_full_w(ws), wphase, abort_flag, 306)) goto done; PROF_ADD(0); }
-                { PROF_T0(); if (!mbar_wait_warp(bar_empty_b(bs), bphase ^ 1, abort_flag, 308)) goto done; PROF_ADD(1); }
-#ifdef Q4B_GEMM2_DEBUG
-                const long long _w0 = clock64();
-#endif
-#ifndef Q4B_GEMM2_NODEQ
+                if (!mbar_wait_warp(bar_full_w(ws), wphase, abort_flag, 306)) goto done;
+                if (!mbar_wait_warp(bar_empty_b(bs), bphase ^ 1, abort_flag, 308)) goto done;
                 if (dw < valid) {
                     const uint32_t wst = base + SMEM_W + ws * w_stage;
                     const uint32_t bst = base + SMEM_B + bs * B_BYTES;
@@ -469,19 +429,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
                         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bst + boff[j]), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
                     }
                 }
-#endif
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(bar_full_b(bs));         // own CTA's barrier; the second CTA's is relayed by its warp 1
                     mbar_arrive(bar_empty_w(ws));
                 }
-#ifdef Q4B_GEMM2_DEBUG
-                prof[2] += clock64() - _w0;
-#endif
             }
         }
-        if (dw == 0 && dgrp == 0) { PROF_FLUSH(6, 3); }
     }
 
 done:
@@ -589,11 +544,3 @@ int gemm2_wait_status(int *value) {
 
 }  // namespace q4b
 
-#ifdef Q4B_GEMM2_DEBUG
-extern "C" __attribute__((visibility("default"))) int q4b_debug_gemm2(unsigned int *out) {
-    return cudaMemcpyFromSymbol(out, q4b::gemm2::g_gemm2_dbg, sizeof(unsigned int) * 8) == cudaSuccess ? 0 : 6;
-}
-extern "C" __attribute__((visibility("default"))) int q4b_debug_gemm2_prof(unsigned long long *out) {
-    return cudaMemcpyFromSymbol(out, q4b::gemm2::g_gemm2_prof, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : 6;
-}
-#endif
