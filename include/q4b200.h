@@ -51,7 +51,7 @@ typedef enum {
     Q4B_ERR_ALIGN = 4,    /* pointer or leading dimension not aligned as documented     */
     Q4B_ERR_ARCH = 5,     /* current device is not compute capability 10.x              */
     Q4B_ERR_CUDA = 6,     /* a CUDA runtime call failed; see q4b_last_cuda_error        */
-    Q4B_ERR_TIMEOUT = 7,  /* a bounded device-side wait gave up (read via q4b_gemm_status) */
+    Q4B_ERR_TIMEOUT = 7,  /* a bounded device-side wait gave up (read via q4b_wait_status) */
     Q4B_ERR_TOO_LARGE = 8 /* problem exceeds a fixed internal buffer                    */
 } q4b_status;
 
@@ -70,16 +70,7 @@ enum {
      * earlier work on the stream is still running, and waits for that work before it reads x
      * or writes y.  Only valid when nothing still in flight on the stream writes `prepacked`. */
     Q4B_FLAG_PDL = 1,
-    /* M = 1 only: run the decode on the 5th-generation tensor cores, weights dequantised into
-     * tensor memory (tcgen05.st / tcgen05.mma), instead of the default mma.sync kernel.  Same
-     * results within the path's tolerance; measured slower on the shapes benchmarked so far, kept
-     * selectable for comparison.  Ignored (default kernel used) for shapes it does not cover. */
-    Q4B_FLAG_DECODE_TMEM = 2,
-    /* M > 128 only: run the prefill on CTA pairs (tcgen05.mma.cta_group::2, each CTA of a two-CTA
-     * cluster loads half of the X tile and dequantises half of the tile's columns) instead of the
-     * default one-CTA kernel.  Same results within the path's tolerance; measured equal or slower
-     * on the shapes benchmarked so far, kept selectable for comparison. */
-    Q4B_FLAG_GEMM_PAIR = 4,
+    /* bits 2 and 4 are not used */
     /* Activation applied to the fp32 result (after the addend, before the one rounding), as the
      * reference's fused kernels matmul_int4_silu / matmul_int4_gelu do (quant_kernels.metal:880-1144):
      * SiLU v / (1 + exp(-v)), or GELU in its tanh form.  At most one of the two. */
@@ -130,7 +121,10 @@ Q4B_API int q4b_dequantize(const void *blocks, int64_t K, int64_t N, void *w_out
  *              warp-level mma + split-K reduction in the CTA.
  *   q4b_gemm   prefill path, any M >= 1 (intended for M >= 17): TMA -> shared memory ->
  *              dequantise to bf16/fp16 -> tcgen05.mma with TMEM accumulators.
- *   q4b_matmul picks q4b_gemv for M <= 16, otherwise q4b_gemm.
+ *   q4b_matmul picks q4b_gemv for M <= 8, and for 9 <= M <= 16 when the weight has fewer than
+ *              2^25 elements; otherwise q4b_gemm (which itself runs a tensor-memory kernel with the
+ *              weights as the tcgen05 A operand for M <= 128).
+ * A flags word with both activation bits set is rejected with Q4B_ERR_ARG.
  */
 Q4B_API int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
              int64_t K, int64_t N, void *y, int64_t ldy, int flags, void *stream);
@@ -142,7 +136,7 @@ Q4B_API int q4b_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const
 /*
  * The same products with an optional fp32 term added before the single rounding to the output
  * dtype: Y = round(X . dequant(W) + addend), addend [M, N] fp32 with leading dimension ld_add
- * (NULL = none).  Used for the group-wise format's zero-point term and for a fused bias
+ * (NULL = none; ld_add = 0: one row of N values added to every row, i.e. a bias).  Used for the group-wise format's zero-point term and for a fused bias
  * (the reference adds its bias after the matmul, quantization.py:602-603).
  */
 Q4B_API int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
@@ -186,6 +180,63 @@ Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
                              int64_t K, int64_t N, int64_t group, float *addend_out, void *stream);
 
 /*
+ * Single-row decode (M = 1) over a list of stages in ONE persistent launch (no reference
+ * counterpart: the reference launches its 64x32-tile kernel once per product,
+ * core_mps.mm:5917-5975, quant_kernels.metal:1738-1886).
+ *
+ * A stage is 1..Q4B_CHAIN_MAX_PRODUCTS products that share one input row of K elements
+ * (q|k|v, gate|up):  y_p = act(alpha_p * (x . dequant(W_p)) + addend_p).  Its input is either a
+ * device pointer whose contents are ready when the launch starts (x != NULL), or the output of an
+ * EARLIER stage's product (x == NULL; x_stage, x_product), optionally transformed on the way in:
+ * Q4B_CHAIN_X_SILU_MUL takes x = silu(a) * b from two earlier outputs (the gated MLP).  Outputs
+ * are always also written to y for the caller.
+ *
+ * Arithmetic: x is held as 15-bit fixed point per 32-k block (scale max|x|/16383), the dot
+ * product with the 4-bit weights is exact in int32 on the tensor cores (mma.sync s8), scales are
+ * applied in fp32, fixed summation order (bitwise repeatable); relative error about 1e-4.
+ *
+ *   q4b_gemv_grouped           one stage, input in plain memory, no workspace.
+ *   q4b_chain_workspace_bytes  size of the device workspace of a chain (0 on bad arguments).
+ *   q4b_chain_build            validates the list, writes the device-side work list and the
+ *                              hand-over buffers into `workspace` (256-byte aligned) and waits for
+ *                              its copies; do it once, outside any stream capture.
+ *   q4b_chain_run              one launch over the whole list; n_stages, x_dtype (f16/bf16, of
+ *                              every input and output) and max_k (largest K of the list) as
+ *                              given to the build.  Launches of one workspace must not overlap on
+ *                              the GPU; weights, outputs and addends must stay where they were.
+ * K a multiple of 32 and at most about 32768 (the input row must fit in shared memory,
+ * Q4B_ERR_TOO_LARGE beyond).  Hand-over waits are bounded like every other wait (q4b_wait_status
+ * codes 500-502).
+ */
+#define Q4B_CHAIN_MAX_PRODUCTS 4
+#define Q4B_CHAIN_MAX_STAGES 256
+enum { Q4B_CHAIN_X_PLAIN = 0, Q4B_CHAIN_X_SILU_MUL = 1 };
+typedef struct {
+    const void *prepacked;  /* [K, N] weights in the streaming layout                        */
+    void *y;                /* [N] output, dtype of the chain                                 */
+    const float *addend;    /* optional fp32 [N] added before the rounding (bias), or NULL   */
+    int64_t N;
+    float alpha;            /* scale of the product, applied in fp32                          */
+    int flags;              /* Q4B_FLAG_ACT_SILU / Q4B_FLAG_ACT_GELU or 0                     */
+} q4b_chain_product;
+typedef struct {
+    const void *x;          /* [K] input in device memory, or NULL: taken from an earlier stage */
+    int x_stage, x_product; /* with x == NULL: which earlier output is the input              */
+    int x_stage2, x_product2; /* with Q4B_CHAIN_X_SILU_MUL: the second operand b              */
+    int xform;              /* Q4B_CHAIN_X_*                                                  */
+    int n_products;
+    int64_t K;
+    q4b_chain_product products[Q4B_CHAIN_MAX_PRODUCTS];
+} q4b_chain_stage;
+Q4B_API int q4b_gemv_grouped(const void *x, int x_dtype, int64_t K, const q4b_chain_product *products,
+                             int n_products, int flags, void *stream);
+Q4B_API size_t q4b_chain_workspace_bytes(const q4b_chain_stage *stages, int n_stages);
+Q4B_API int q4b_chain_build(const q4b_chain_stage *stages, int n_stages, void *workspace,
+                            size_t workspace_bytes, void *stream);
+Q4B_API int q4b_chain_run(const void *workspace, int n_stages, int x_dtype, int64_t max_k, int flags,
+                          void *stream);
+
+/*
  * Decode product with a fused all-gather (column-parallel layers over several GPUs of one box; no
  * reference counterpart, the reference is single-device): q4b_gemv, but each rank's kernel stores
  * its [M, N] result at column offset col0 of the [M, ld_out] output of EVERY rank, through
@@ -210,8 +261,8 @@ Q4B_API int q4b_rmsnorm(const void *x, int dtype, int64_t M, int64_t K, int64_t 
  * The matmul kernels bound every mbarrier wait; a wait that gives up makes the kernel set a
  * status word on the device and stop early (its output is then incomplete).  This call
  * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with
- * *detail (may be NULL) = which wait gave up (1..8 prefill kernel roles, 100-102 decode kernels,
- * 201-206 tensor-memory decode kernel, 301-309 CTA-pair prefill kernel).
+ * *detail (may be NULL) = which wait gave up (1..8 prefill kernel roles, 100-101 decode kernels,
+ * 401-407 small-batch tensor-memory kernel, 500-502 persistent single-row kernel).
  * It never traps or faults the device.
  */
 Q4B_API int q4b_wait_status(void *stream, int *detail);

@@ -15,12 +15,27 @@ LIB_PATH = os.path.join(_HERE, "libq4b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 LAYOUT_KN, LAYOUT_NK = 0, 1
-FLAG_NONE, FLAG_PDL, FLAG_DECODE_TMEM, FLAG_GEMM_PAIR, FLAG_ACT_SILU, FLAG_ACT_GELU = 0, 1, 2, 4, 8, 16
+FLAG_NONE, FLAG_PDL, FLAG_ACT_SILU, FLAG_ACT_GELU = 0, 1, 8, 16
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_ARCH, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(9)
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 _i64, _vp, _ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+
+CHAIN_MAX_PRODUCTS = 4
+CHAIN_X_PLAIN, CHAIN_X_SILU_MUL = 0, 1
+
+
+class ChainProduct(ctypes.Structure):
+    """q4b_chain_product of include/q4b200.h."""
+    _fields_ = [("prepacked", _vp), ("y", _vp), ("addend", _vp), ("N", _i64), ("alpha", ctypes.c_float), ("flags", _ci)]
+
+
+class ChainStage(ctypes.Structure):
+    """q4b_chain_stage of include/q4b200.h."""
+    _fields_ = [("x", _vp), ("x_stage", _ci), ("x_product", _ci), ("x_stage2", _ci), ("x_product2", _ci),
+                ("xform", _ci), ("n_products", _ci), ("K", _i64), ("products", ChainProduct * CHAIN_MAX_PRODUCTS)]
+
 
 # every symbol include/q4b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
@@ -38,6 +53,10 @@ SYMBOLS = {
     "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
     "q4b_gemv_gather": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _vp]),
+    "q4b_gemv_grouped": (_ci, [_vp, _ci, _i64, ctypes.POINTER(ChainProduct), _ci, _ci, _vp]),
+    "q4b_chain_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(ChainStage), _ci]),
+    "q4b_chain_build": (_ci, [ctypes.POINTER(ChainStage), _ci, _vp, ctypes.c_size_t, _vp]),
+    "q4b_chain_run": (_ci, [_vp, _ci, _ci, _i64, _ci, _vp]),
     "q4b_rmsnorm": (_ci, [_vp, _ci, _i64, _i64, _i64, _vp, ctypes.c_float, _vp, _i64, _vp]),
     "q4b_matmul_host": (_ci, [_vp, _vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp, _ci, _vp]),
     "q4b_matmul_host_noalloc": (_ci, [_vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp]),

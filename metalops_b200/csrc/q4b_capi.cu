@@ -1,7 +1,6 @@
 // C-ABI glue: status strings, device checks, the M-based dispatcher and the host-buffer
 // convenience entry.  The kernels live in q4b_quantize.cu, q4b_gemv.cu and q4b_gemm_sm100.cu.
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -44,39 +43,6 @@ static const DevInfo *dev_info() {
 int device_sm_count() {
     const DevInfo *d = dev_info();
     return d ? d->sms : 148;
-}
-
-// Q4B_GEMV_KSPLIT=1|2|4|8 forces the decode kernel's k-split (benchmark sweeps only).
-int gemv_ksplit_override() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("Q4B_GEMV_KSPLIT");
-        int k = e ? atoi(e) : 0;
-        v = (k == 1 || k == 2 || k == 4 || k == 8) ? k : 0;
-    }
-    return v;
-}
-
-// Q4B_GEMV_GEOM=<tiles per slot><slots> (82, 83, 43, 42, 44) forces the decode kernel's ring
-// geometry for M = 1 (benchmark sweeps only).
-int gemv_geom_override() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("Q4B_GEMV_GEOM");
-        const int k = e ? atoi(e) : 0;
-        v = (k == 82 || k == 43 || k == 42 || k == 44 || k == 83 || k == 22 || k == 23) ? k : 0;
-    }
-    return v;
-}
-
-// Q4B_GEMV_TC=0/1 forces the tensor-memory decode kernel off / on for M = 1 (benchmark sweeps only).
-int gemv_tc_override() {
-    static int v = -2;
-    if (v == -2) {
-        const char *e = getenv("Q4B_GEMV_TC");
-        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
-    }
-    return v;
 }
 
 }  // namespace q4b

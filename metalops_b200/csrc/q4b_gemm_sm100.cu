@@ -22,7 +22,6 @@
 // a CTA-wide abort flag and every role leaves through the common exit that frees TMEM.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "q4b_common.cuh"
@@ -37,13 +36,7 @@ constexpr int A_BYTES = BM * BK * 2;                 // 32768
 constexpr int A_HALF_BYTES = HALF_M * BK * 2;        // 16384
 constexpr int B_BYTES = BN * BK * 2;                 // 32768
 constexpr int W_TILES = BN / TILE_N;                 // 16 prepacked tiles per step
-#ifndef Q4B_GEMM_DEQ_WARPS
-#define Q4B_GEMM_DEQ_WARPS 8
-#endif
-#ifndef Q4B_GEMM_WARP_POLL
-#define Q4B_GEMM_WARP_POLL 0
-#endif
-constexpr int NUM_DEQ_WARPS = Q4B_GEMM_DEQ_WARPS;    // prepacked tiles of a step are dealt round-robin to these warps
+constexpr int NUM_DEQ_WARPS = 8;                     // prepacked tiles of a step are dealt round-robin to these warps
 constexpr int WARP_A = 0, WARP_MMA = 1, WARP_W = 6, FIRST_DEQ_WARP = 7;   // warps 2..5: epilogue
 constexpr int FIRST_EPI2_WARP = FIRST_DEQ_WARP + NUM_DEQ_WARPS;   // four more epilogue warps
 constexpr int THREADS = (FIRST_EPI2_WARP + 4) * 32;              // 608
@@ -65,15 +58,6 @@ __host__ __device__ inline int w_ring_depth(int bn) {
 constexpr long long WAIT_LIMIT_CYCLES = 1LL << 28;   // ~0.15 s; far above any legitimate wait
 
 __device__ int g_gemm_status = 0;
-#ifdef Q4B_GEMM_PROFILE
-// development aid: per-CTA cycle counters of where the roles wait (read with cudaMemcpyFromSymbol)
-__device__ long long g_gemm_prof[148 * 8];
-#define PROF_T0() const long long _pt = clock64()
-#define PROF_ADD(slot) prof[slot] += clock64() - _pt
-#else
-#define PROF_T0()
-#define PROF_ADD(slot)
-#endif
 
 // ---- thin PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -115,20 +99,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
 }
-// Whole-warp wait with one polling lane: lane 0 polls, the others sleep at the warp barrier and
-// then observe the completed phase themselves with a single try_wait.
+// Whole-warp wait: every lane polls (one polling lane plus a warp barrier measured no faster).
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code, int lane) {
-#if Q4B_GEMM_WARP_POLL
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait<SLEEP_NS>(bar, parity, abort_flag, code);
-    __syncwarp();
-    if (lane != 0) ok = mbar_try_wait(bar, parity);
-    return __all_sync(0xffffffffu, ok);
-#else
     (void)lane;
     return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag, code));
-#endif
 }
 // true on one lane of the (converged) warp
 __device__ __forceinline__ bool elect_one() {
@@ -307,18 +282,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
             const uint32_t idesc = make_idesc(BF16, HALF_M, bn);
             RingPos a, b;
             uint32_t tphase = 0;
-#ifdef Q4B_GEMM_PROFILE
-            long long prof[4] = {0, 0, 0, 0};
-            const long long prof_start = clock64();
-#endif
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 const int mt = t % num_mt;
                 const int halves = (M - mt * BM > HALF_M) ? 2 : 1;     // skip an all-padding lower half
-                { PROF_T0(); if (!mbar_wait_warp(bar_tempty, tphase ^ 1, abort_flag, 2, lane)) goto done; PROF_ADD(0); }
+                if (!mbar_wait_warp(bar_tempty, tphase ^ 1, abort_flag, 2, lane)) goto done;
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    { PROF_T0(); if (!mbar_wait_warp(bar_full_a(a.s), a.phase, abort_flag, 3, lane)) goto done; PROF_ADD(1); }
-                    { PROF_T0(); if (!mbar_wait_warp(bar_full_b(b.s), b.phase, abort_flag, 4, lane)) goto done; PROF_ADD(2); }
+                    if (!mbar_wait_warp(bar_full_a(a.s), a.phase, abort_flag, 3, lane)) goto done;
+                    if (!mbar_wait_warp(bar_full_b(b.s), b.phase, abort_flag, 4, lane)) goto done;
                     tc_fence_after();
                     if (elect_one()) {
                         const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_B + b.s * B_BYTES);
@@ -338,14 +309,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                 }
                 tphase ^= 1;
             }
-#ifdef Q4B_GEMM_PROFILE
-            if (lane == 0 && blockIdx.x < 148) {
-                g_gemm_prof[blockIdx.x * 8 + 0] = prof[0];
-                g_gemm_prof[blockIdx.x * 8 + 1] = prof[1];
-                g_gemm_prof[blockIdx.x * 8 + 2] = prof[2];
-                g_gemm_prof[blockIdx.x * 8 + 3] = clock64() - prof_start;
-            }
-#endif
         }
     } else if (warp < WARP_W || warp >= FIRST_EPI2_WARP) {
         // ---------------- epilogue: two warps per TMEM lane quadrant, alternate 32-column chunks ----
@@ -416,17 +379,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         const uint32_t doff = (uint32_t)(dw * TILE_BYTES + TILE_QS_BYTES + g * 8);
         constexpr int TILES_PER_WARP = W_TILES / NUM_DEQ_WARPS;      // tile dw + i*NUM_DEQ_WARPS, i < TILES_PER_WARP
         RingPos w, b;
-#ifdef Q4B_GEMM_PROFILE
-        long long prof[4] = {0, 0, 0, 0};
-#endif
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             const int valid = min(w_tiles, NT - (t / num_mt) * w_tiles);
             for (int ks = 0; ks < k_steps; ++ks) {
-                { PROF_T0(); if (!mbar_wait_warp(bar_full_w(w.s), w.phase, abort_flag, 6, lane)) goto done; PROF_ADD(0); }
-                { PROF_T0(); if (!mbar_wait_warp(bar_empty_b(b.s), b.phase ^ 1, abort_flag, 8, lane)) goto done; PROF_ADD(1); }
-#ifdef Q4B_GEMM_PROFILE
-                const long long _work0 = clock64();
-#endif
+                if (!mbar_wait_warp(bar_full_w(w.s), w.phase, abort_flag, 6, lane)) goto done;
+                if (!mbar_wait_warp(bar_empty_b(b.s), b.phase ^ 1, abort_flag, 8, lane)) goto done;
 #pragma unroll
                 for (int i = 0; i < TILES_PER_WARP; ++i) {
                     if (dw + i * NUM_DEQ_WARPS >= valid) break;
@@ -461,20 +418,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                     mbar_arrive(bar_full_b(b.s));
                     mbar_arrive(bar_empty_w(w.s));
                 }
-#ifdef Q4B_GEMM_PROFILE
-                prof[2] += clock64() - _work0;
-#endif
                 w.advance(sw);
                 b.advance(SB);
             }
         }
-#ifdef Q4B_GEMM_PROFILE
-        if (dw == 0 && lane == 0 && blockIdx.x < 148) {
-            g_gemm_prof[blockIdx.x * 8 + 4] = prof[0];
-            g_gemm_prof[blockIdx.x * 8 + 5] = prof[1];
-            g_gemm_prof[blockIdx.x * 8 + 6] = prof[2];
-        }
-#endif
     }
 
 done:
@@ -524,9 +471,17 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
         const long cost = ((t + sms - 1) / sms) * (cand + 24);
         if (best < 0 || cost < best) { best = cost; bn = cand; }
     }
-    if (const char *e = getenv("Q4B_GEMM_BN")) { const int v = atoi(e); if (v >= 32 && v <= BN && v % 32 == 0) bn = v; }
-    // per call: the attribute is per device and a process may drive several
-    Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    {   // opt in to the large dynamic shared memory once per device and instantiation
+        static bool attr_done[64] = {};
+        static std::mutex attr_mu;
+        int dev = 0;
+        Q4B_CUDA_TRY(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> attr_lock(attr_mu);
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
     const int tiles = mt * ((N + bn - 1) / bn);
     const int grid = tiles < sms ? tiles : sms;
     gemm_tcgen05_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K,
@@ -539,32 +494,10 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
 
 int device_sm_count();
 int gemv_wait_status(int *value);
-int gemv_tc_wait_status(int *value);
-int gemm2_wait_status(int *value);
-int gemm2_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int K, int N, const float *addend,
-                 int64_t ld_add, void *y, int64_t ldy, int act, cudaStream_t st);
 int gemm_tmem_wait_status(int *value);
+namespace chain { int wait_status(int *value); }
 int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
                      const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
-// Q4B_GEMM_TMEM=0/1 forces the small-batch tensor-memory kernel off / on for M <= 128 (benchmark sweeps only)
-static int gemm_tmem_override() {
-    static int v = -2;
-    if (v == -2) {
-        const char *e = getenv("Q4B_GEMM_TMEM");
-        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
-    }
-    return v;
-}
-// Q4B_GEMM_PAIR=0/1 forces the CTA-pair prefill kernel off / on (benchmark sweeps only)
-static int gemm_pair_override() {
-    static int v = -2;
-    if (v == -2) {
-        const char *e = getenv("Q4B_GEMM_PAIR");
-        v = e ? (atoi(e) != 0 ? 1 : 0) : -1;
-    }
-    return v;
-}
-
 }  // namespace q4b
 
 using namespace q4b;
@@ -577,9 +510,11 @@ extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, cons
 extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                                int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
                                void *stream) {
-    if (addend != nullptr && ld_add < N) return Q4B_ERR_ARG;
+    // ld_add == 0: the addend is one row of N values added to every row of the result (a bias)
+    if (addend != nullptr && ld_add != 0 && ld_add < N) return Q4B_ERR_ARG;
     if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
+    if (act_of_flags(flags) == 3) return Q4B_ERR_ARG;
     if (K % QK || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return Q4B_ERR_SHAPE;
     if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
     if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
@@ -587,14 +522,9 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
     // Up to 128 rows: the tensor-memory kernel (weights as the A operand), whose step cost does not
     // depend on M, unless the weight has more 128-column panels than two per SM (it is not
     // persistent: several waves of CTAs each pay its prologue and reduction).
-    int use_tmem = gemm_tmem_override();
-    if (use_tmem < 0) use_tmem = ceil_div(tiles_n(N), 8) <= 2 * device_sm_count() ? 1 : 0;
-    if (M <= 128 && use_tmem == 1)
+    if (M <= 128 && ceil_div(tiles_n(N), 8) <= 2 * device_sm_count())
         return gemm_tmem_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags,
                                 (cudaStream_t)stream);
-    if (gemm_pair_override() == 1 || ((flags & Q4B_FLAG_GEMM_PAIR) && gemm_pair_override() != 0 && M > gemm::HALF_M))
-        return gemm2_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, (int)K, (int)N, addend, ld_add, y, ldy,
-                            act_of_flags(flags), (cudaStream_t)stream);
     gemm::EncodeTiledFn enc = gemm::get_encode_fn();
     if (enc == nullptr) return Q4B_ERR_CUDA;
 
@@ -618,11 +548,6 @@ extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ld
                                      act_of_flags(flags), st);
 }
 
-#ifdef Q4B_GEMM_PROFILE
-extern "C" __attribute__((visibility("default"))) int q4b_debug_gemm_profile(long long *out) {
-    return cudaMemcpyFromSymbol(out, gemm::g_gemm_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 6;
-}
-#endif
 
 extern "C" int q4b_wait_status(void *stream, int *detail) {
     Q4B_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
@@ -634,11 +559,9 @@ extern "C" int q4b_wait_status(void *stream, int *detail) {
     }
     if (int rc = gemv_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
-    if (int rc = gemv_tc_wait_status(&hv)) return rc;
-    if (h == 0) h = hv;
-    if (int rc = gemm2_wait_status(&hv)) return rc;
-    if (h == 0) h = hv;
     if (int rc = gemm_tmem_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = chain::wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (detail) *detail = h;
     return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;

@@ -21,7 +21,7 @@
 //     and activation and writes Y row-major with coalesced stores.
 // Every mbarrier wait is bounded; a wait that gives up records a code and all roles fall through
 // to the common exit.
-#include <cstdlib>
+#include <mutex>
 #include <mutex>
 
 #include "q4b_sm100_ptx.cuh"
@@ -311,10 +311,19 @@ static int choose_ksplit(int64_t panels, int64_t KU, int sms) {
 template <bool BF16>
 static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t K, int64_t N, void *y, int64_t ldy,
                   const float *addend, int64_t ld_add, int rows, int act, int flags, int sms, cudaStream_t st) {
-    Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_tmem_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    {   // opt in to the large dynamic shared memory once per device and instantiation
+        static bool attr_done[64] = {};
+        static std::mutex attr_mu;
+        int dev = 0;
+        Q4B_CUDA_TRY(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> attr_lock(attr_mu);
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_tmem_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
     const int64_t panels = ceil_div(tiles_n(N), PANEL_TILES);
     int ks = choose_ksplit(panels, tiles_k(K), sms);
-    if (const char *e = getenv("Q4B_GEMM_TMEM_KSPLIT")) { const int v = atoi(e); if (v >= 1 && v <= 8 && v <= tiles_k(K)) ks = v; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(panels * ks));
     cfg.blockDim = dim3(THREADS);

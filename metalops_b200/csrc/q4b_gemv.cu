@@ -19,7 +19,7 @@
 //
 // Every mbarrier wait is bounded: a wait that gives up sets g_wait_status and the warp stops
 // consuming (its outputs are then wrong, which the status reports) instead of spinning.
-#include <cstdlib>
+#include <mutex>
 
 #include "q4b_common.cuh"
 
@@ -39,22 +39,7 @@ struct PeerOut {
     int world;
     int64_t col0, ld;
 };
-static thread_local PeerOut tl_peers = {};          // set by q4b_gemv_gather around the dispatch
 
-#ifdef Q4B_GEMV_TRACE
-// development aid: one record per CTA (weights pointer, block | sm << 32, four global-timer stamps)
-constexpr int TRACE_MAX = 1 << 16;
-__device__ unsigned long long g_trace[TRACE_MAX * 6];
-__device__ unsigned int g_trace_n = 0;
-__device__ __forceinline__ unsigned long long trace_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TRACE_STAMP(i) if (threadIdx.x == 0) trace_t[i] = trace_now()
-#else
-#define TRACE_STAMP(i)
-#endif
 
 // Shared-memory geometry of one ring slot: CHUNK weight tiles, then the x rows.  The row
 // stride is 64 bytes more than a multiple of 128 so that the eight (row, k-octet) pairs a
@@ -383,13 +368,15 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 
 template <bool BF16, int MF, int KS, int CHUNK, int SLOTS, bool GATHER>
 static int launch_gemv_impl(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
-                            int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
+                            int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st, const PeerOut &po) {
     constexpr int NTC = GEMV_WARPS / KS;
     const int smem = GEMV_WARPS * SLOTS * SlotGeom<CHUNK>::slot_bytes(M);
     // opt in to > 48 KB of dynamic shared memory once per device and instantiation
     static bool attr_done[64] = {};
+    static std::mutex attr_mu;
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> attr_lock(attr_mu);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<BF16, MF, KS, CHUNK, SLOTS, GATHER>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -407,16 +394,16 @@ static int launch_gemv_impl(const void *x, int M, int64_t ldx, const void *prepa
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<BF16, MF, KS, CHUNK, SLOTS, GATHER>, (const uint16_t *)x, M, ldx,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add, act_of_flags(flags), tl_peers));
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, ldy, addend, ld_add, act_of_flags(flags), po));
     return Q4B_OK;
 }
 // the fused all-gather is its own instantiation, so that the plain kernel carries none of it
 template <bool BF16, int MF, int KS, int CHUNK, int SLOTS>
 static int launch_gemv(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
-                       int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
-    return tl_peers.world != 0
-               ? launch_gemv_impl<BF16, MF, KS, CHUNK, SLOTS, true>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st)
-               : launch_gemv_impl<BF16, MF, KS, CHUNK, SLOTS, false>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+                       int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st, const PeerOut &po) {
+    return po.world != 0
+               ? launch_gemv_impl<BF16, MF, KS, CHUNK, SLOTS, true>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po)
+               : launch_gemv_impl<BF16, MF, KS, CHUNK, SLOTS, false>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
 }
 
 // ---- single activation row ---------------------------------------------------------------
@@ -445,10 +432,6 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
     __shared__ __align__(8) uint64_t bars[GEMV_WARPS][SLOTS];
     __shared__ float red[GEMV_WARPS][TILE_N];
 
-#ifdef Q4B_GEMV_TRACE
-    unsigned long long trace_t[4] = {0, 0, 0, 0};
-#endif
-    TRACE_STAMP(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int ks = warp % KS, ntl = warp / KS;
@@ -508,7 +491,6 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
     // dependent launch the weight copies above overlap the previous kernel's tail.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TRACE_STAMP(1);
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s)
@@ -552,9 +534,6 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
             for (int s = 0; s < SLOTS; ++s) {
                 if (ok && ci < nfull) {
                     ok = wait_slot(bar_s + 8u * s, parity);
-#ifdef Q4B_GEMV_TRACE
-                    if (threadIdx.x == 0 && trace_t[2] == 0) trace_t[2] = trace_now();
-#endif
                     if (ok) {
                         m1_consume<BF16, CHUNK, true>(q0, d0, xs, xown, (uint32_t)(s * G::SLOT_BYTES), c, CHUNK, acc);
                         __syncwarp();            // every lane has read the slot before it is refilled
@@ -608,30 +587,19 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
             }
         }
     }
-#ifdef Q4B_GEMV_TRACE
-    TRACE_STAMP(3);
-    if (threadIdx.x == 0) {
-        const unsigned int i = atomicAdd(&g_trace_n, 1u);
-        if (i < (unsigned)TRACE_MAX) {
-            unsigned int smid;
-            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            g_trace[i * 6 + 0] = (unsigned long long)prepacked;
-            g_trace[i * 6 + 1] = (unsigned long long)blockIdx.x | ((unsigned long long)smid << 32);
-            for (int j = 0; j < 4; ++j) g_trace[i * 6 + 2 + j] = trace_t[j];
-        }
-    }
-#endif
 }
 
 template <bool BF16, int KS, int CHUNK, int SLOTS, bool GATHER>
 static int launch_gemv_m1_impl(const void *x, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend,
-                               int flags, cudaStream_t st) {
+                               int flags, cudaStream_t st, const PeerOut &po) {
     using G = M1Geom<CHUNK, SLOTS>;
     constexpr int NTC = GEMV_WARPS / KS;
     // opt in to > 48 KB of dynamic shared memory once per device and instantiation
     static bool attr_done[64] = {};
+    static std::mutex attr_mu;
     int dev = 0;
     Q4B_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> attr_lock(attr_mu);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         Q4B_CUDA_TRY(cudaFuncSetAttribute(gemv_m1_kernel<BF16, KS, CHUNK, SLOTS, GATHER>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, G::RING_BYTES));
@@ -648,21 +616,20 @@ static int launch_gemv_m1_impl(const void *x, const void *prepacked, int64_t K, 
     cfg.attrs = attr;
     cfg.numAttrs = (flags & Q4B_FLAG_PDL) ? 1 : 0;
     Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_m1_kernel<BF16, KS, CHUNK, SLOTS, GATHER>, (const uint16_t *)x,
-                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend, act_of_flags(flags), tl_peers));
+                                    (const uint8_t *)prepacked, K, N, (uint16_t *)y, addend, act_of_flags(flags), po));
     return Q4B_OK;
 }
 template <bool BF16, int KS, int CHUNK, int SLOTS>
 static int launch_gemv_m1(const void *x, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend,
-                          int flags, cudaStream_t st) {
-    return tl_peers.world != 0 ? launch_gemv_m1_impl<BF16, KS, CHUNK, SLOTS, true>(x, prepacked, K, N, y, addend, flags, st)
-                               : launch_gemv_m1_impl<BF16, KS, CHUNK, SLOTS, false>(x, prepacked, K, N, y, addend, flags, st);
+                          int flags, cudaStream_t st, const PeerOut &po) {
+    return po.world != 0 ? launch_gemv_m1_impl<BF16, KS, CHUNK, SLOTS, true>(x, prepacked, K, N, y, addend, flags, st, po)
+                               : launch_gemv_m1_impl<BF16, KS, CHUNK, SLOTS, false>(x, prepacked, K, N, y, addend, flags, st, po);
 }
 
 // Ring geometry by row count: shared memory per CTA = 8 warps x SLOTS x (CHUNK x 576 + M x row).
 //   M <= 4 : 8 tiles x 2 slots or 4 tiles x 3 slots (see below)
 //   M <= 8 : 4 tiles x 2 slots (100 KB)          M <= 16 : 2 tiles x 2 slots (98 KB)
 int device_sm_count();
-int gemv_geom_override();
 
 // Single-row launches: k-split and ring geometry by the number of column tiles NT.  A chain of
 // decode launches runs fastest when each is one wave of CTAs (the next launch's CTAs then load
@@ -680,16 +647,15 @@ static int m1_geometry(int64_t NT, int ks, int sms) {
 
 template <bool BF16, int KS>
 static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, void *y,
-                         int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
+                         int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st, const PeerOut &po) {
     if (M == 1) {
         // one row: the eight mma columns carry eight 32-k blocks (see m1_consume)
         int geom = m1_geometry(tiles_n(N), KS, device_sm_count());
-        if (const int o = gemv_geom_override()) geom = o;
         switch (geom) {
-            case 43: return launch_gemv_m1<BF16, KS, 4, 3>(x, prepacked, K, N, y, addend, flags, st);
-            case 42: return launch_gemv_m1<BF16, KS, 4, 2>(x, prepacked, K, N, y, addend, flags, st);
-            case 44: return launch_gemv_m1<BF16, KS, 4, 4>(x, prepacked, K, N, y, addend, flags, st);
-            default: return launch_gemv_m1<BF16, KS, 8, 2>(x, prepacked, K, N, y, addend, flags, st);
+            case 43: return launch_gemv_m1<BF16, KS, 4, 3>(x, prepacked, K, N, y, addend, flags, st, po);
+            case 42: return launch_gemv_m1<BF16, KS, 4, 2>(x, prepacked, K, N, y, addend, flags, st, po);
+            case 44: return launch_gemv_m1<BF16, KS, 4, 4>(x, prepacked, K, N, y, addend, flags, st, po);
+            default: return launch_gemv_m1<BF16, KS, 8, 2>(x, prepacked, K, N, y, addend, flags, st, po);
         }
     }
     // Several rows: slot bytes grow with M (the slot carries the rows' x slices), so the ring gets
@@ -699,38 +665,30 @@ static int launch_gemv_m(const void *x, int M, int64_t ldx, const void *prepacke
     int geom = M <= 8 ? 42 : 22;
     if (M == 2) geom = m1_geometry(tiles_n(N), KS, device_sm_count());
     if (M <= 8) {
-        if (const int o = gemv_geom_override()) geom = o;
         switch (geom) {
-            case 82: return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 43: return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 23: return launch_gemv<BF16, 1, KS, 2, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            case 22: return launch_gemv<BF16, 1, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-            default: return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+            case 82: return launch_gemv<BF16, 1, KS, 8, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+            case 43: return launch_gemv<BF16, 1, KS, 4, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+            case 23: return launch_gemv<BF16, 1, KS, 2, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+            case 22: return launch_gemv<BF16, 1, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+            default: return launch_gemv<BF16, 1, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
         }
     }
-    if (const int o = gemv_geom_override()) geom = o;
-    if (geom == 23) return launch_gemv<BF16, 2, KS, 2, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-    if (geom == 42) return launch_gemv<BF16, 2, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-    return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    if (geom == 23) return launch_gemv<BF16, 2, KS, 2, 3>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+    if (geom == 42) return launch_gemv<BF16, 2, KS, 4, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+    return launch_gemv<BF16, 2, KS, 2, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
 }
 
 template <bool BF16>
 static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
-                          void *y, int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st) {
+                          void *y, int64_t ldy, const float *addend, int64_t ld_add, int flags, cudaStream_t st, const PeerOut &po) {
     switch (ksplit) {
-        case 8: return launch_gemv_m<BF16, 8>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-        case 4: return launch_gemv_m<BF16, 4>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-        case 2: return launch_gemv_m<BF16, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
-        default: return launch_gemv_m<BF16, 1>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+        case 8: return launch_gemv_m<BF16, 8>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+        case 4: return launch_gemv_m<BF16, 4>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+        case 2: return launch_gemv_m<BF16, 2>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+        default: return launch_gemv_m<BF16, 1>(x, M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
     }
 }
 
-int device_sm_count();
-int gemv_ksplit_override();
-int gemv_tc_override();
-int gemv_tc_ksplit(int64_t K, int64_t N, int sms);
-int gemv_tc_launch(const void *x, int bf16, const void *prepacked, int64_t K, int64_t N, void *y, const float *addend, int ks,
-                   int flags, cudaStream_t st);
 
 // read and clear this file's wait status (host side; the caller has synchronised the stream)
 int gemv_wait_status(int *value) {
@@ -748,46 +706,37 @@ int gemv_wait_status(int *value) {
 
 using namespace q4b;
 
-#ifdef Q4B_GEMV_TRACE
-// copies the trace records out (returns their number) and clears the trace
-extern "C" __attribute__((visibility("default"))) int q4b_debug_gemv_trace(unsigned long long *out, int max_records) {
-    unsigned int n = 0;
-    if (cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n)) != cudaSuccess) return -1;
-    if (n > (unsigned)TRACE_MAX) n = TRACE_MAX;
-    if ((int)n > max_records) n = (unsigned)max_records;
-    if (n && cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 6 * n) != cudaSuccess) return -1;
-    const unsigned int zero = 0;
-    cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
-    return (int)n;
-}
-#endif
 
 extern "C" int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
                         int64_t N, void *y, int64_t ldy, int flags, void *stream) {
     return q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y, ldy, flags, stream);
 }
 
-extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
-                               int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
-                               void *stream) {
-    if (addend != nullptr && ld_add < N) return Q4B_ERR_ARG;
+// argument checks and launch plan shared by the plain and the gathering entry points
+static int gemv_dispatch(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                         const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, void *stream,
+                         const PeerOut &po) {
+    // ld_add == 0: the addend is one row of N values added to every row of the result (a bias)
+    if (addend != nullptr && ld_add != 0 && ld_add < N) return Q4B_ERR_ARG;
     if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
     if (M > 16 || K % QK || tiles_k(K) > (1 << 24)) return Q4B_ERR_SHAPE;
     if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    if (act_of_flags(flags) == 3) return Q4B_ERR_ARG;
     if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
     // k-split (see m1_ksplit for one row), never more splits than k-tiles
     const int64_t NT = tiles_n(N), KU = tiles_k(K);
-    int ks = gemv_ksplit_override();
-    if (ks == 0) ks = M == 1 ? m1_ksplit(NT, device_sm_count()) : 8;     // several rows: always 8 (measured)
+    int ks = M == 1 ? m1_ksplit(NT, device_sm_count()) : 8;             // several rows: always 8 (measured)
     while (ks > 1 && KU < ks) ks /= 2;
     cudaStream_t st = (cudaStream_t)stream;
-    if (M == 1 && tl_peers.world == 0 && (gemv_tc_override() == 1 || ((flags & Q4B_FLAG_DECODE_TMEM) && gemv_tc_override() != 0))) {
-        const int tks = gemv_tc_ksplit(K, N, device_sm_count());
-        if (tks > 0) return gemv_tc_launch(x, x_dtype == Q4B_BF16, prepacked, K, N, y, addend, tks, flags, st);
-    }
-    return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st)
-                               : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st);
+    return x_dtype == Q4B_BF16 ? launch_gemv_ks<true>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po)
+                               : launch_gemv_ks<false>(ks, x, (int)M, ldx, prepacked, K, N, y, ldy, addend, ld_add, flags, st, po);
+}
+
+extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                               int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
+                               void *stream) {
+    return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, stream, PeerOut{});
 }
 
 extern "C" int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
@@ -801,9 +750,6 @@ extern "C" int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ld
     po.world = world;
     po.col0 = col0;
     po.ld = ld_out;
-    tl_peers = po;
     // y itself is not written in this mode; the first rank pointer stands in for the argument checks
-    const int rc = q4b_gemv_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y_ranks[0], ld_out, flags & ~Q4B_FLAG_DECODE_TMEM, stream);
-    tl_peers = PeerOut{};
-    return rc;
+    return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y_ranks[0], ld_out, flags, stream, po);
 }

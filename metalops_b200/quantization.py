@@ -47,6 +47,16 @@ class Q4Prepacked:
         return self.data.numel()
 
 
+def _version_of(t: torch.Tensor):
+    """In-place modification counter used as a cache key.  Inference tensors keep no counter
+    (reading it raises); they cannot be modified in place outside inference mode, so their
+    storage address and shape stand in for it."""
+    try:
+        return t._version
+    except RuntimeError:
+        return ("inference", t.data_ptr(), tuple(t.shape))
+
+
 def _alloc_prepacked(K: int, N: int, device: torch.device) -> torch.Tensor:
     nbytes = _cabi.load().q4b_prepacked_bytes(K, N)
     if nbytes == 0:
@@ -90,14 +100,14 @@ def quantize_ggml_q4_0(weight: torch.Tensor) -> torch.Tensor:
     ``[K/32, N, 18]``.
     """
     blocks, pre = _quantize_impl(weight, True, True)
-    blocks._q4b_prepacked = (blocks._version, pre)
+    blocks._q4b_prepacked = (_version_of(blocks), pre)
     return blocks
 
 
 def prepack_ggml_q4_0(W_blocks: torch.Tensor) -> Q4Prepacked:
     """Streaming-layout copy of ``W_blocks [K/32, N, 18]`` (cached on the tensor object)."""
     cached = getattr(W_blocks, "_q4b_prepacked", None)
-    if cached is not None and cached[0] == W_blocks._version and cached[1].device == W_blocks.device:
+    if cached is not None and cached[0] == _version_of(W_blocks) and cached[1].device == W_blocks.device:
         return cached[1]
     _cabi.require_device(W_blocks, "W_blocks")
     if W_blocks.dtype != torch.uint8 or W_blocks.dim() != 3 or W_blocks.shape[2] != BLOCK_Q4_0_SIZE:
@@ -110,7 +120,7 @@ def prepack_ggml_q4_0(W_blocks: torch.Tensor) -> Q4Prepacked:
     _cabi.check(rc, "prepack_ggml_q4_0")
     out = Q4Prepacked(pre, K, N)
     try:
-        W_blocks._q4b_prepacked = (W_blocks._version, out)
+        W_blocks._q4b_prepacked = (_version_of(W_blocks), out)
     except AttributeError:
         pass
     return out
@@ -286,7 +296,7 @@ class Int4GPrepacked:
 def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int = 128) -> Int4GPrepacked:
     """One-time conversion of a group-wise INT4 weight (cached on ``W_packed``).  Needs
     ``K % 32 == 0`` and ``group_size % 32 == 0``, and scales inside fp16's range."""
-    key = (W_packed._version, scales.data_ptr(), scales._version, zeros.data_ptr(), zeros._version, group_size)
+    key = (_version_of(W_packed), scales.data_ptr(), _version_of(scales), zeros.data_ptr(), _version_of(zeros), group_size)
     cached = getattr(W_packed, "_q4b_int4g", None)
     if cached is not None and cached[0] == key:
         return cached[1]

@@ -142,7 +142,7 @@ def test_matmul_int4_fused_activation(mo, cuda_dev, M, act):
     w = torch.randn(K, N, generator=g) * 0.05
     x = torch.randn(M, K, generator=g).half()
     packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), gs)
-    wd = mo.dequantize_int4(packed, scales, zeros, gs, torch.float32).cpu()
+    wd = orc.dequantize_int4_groupwise(packed.cpu(), scales.cpu(), zeros.cpu(), gs, torch.float32)
     lin = x.float() @ wd
     ref = torch.nn.functional.silu(lin) if act == "silu" else torch.nn.functional.gelu(lin, approximate="tanh")
     fn = mo.matmul_int4_silu if act == "silu" else mo.matmul_int4_gelu
@@ -182,16 +182,15 @@ def test_rmsnorm_and_fused_rmsnorm_linear_int4(mo, cuda_dev, M, dtype):
 
 def test_activation_on_q4_0_kernels_all_paths(mo, cuda_dev):
     """The activation flag on every matmul kernel: single-row and multi-row decode, the
-    tensor-memory decode kernel, the prefill kernel and its CTA-pair variant."""
+    small-batch tensor-memory kernel and the prefill kernel.  Reference weights come from the oracle."""
     from metalops_b200 import _cabi, quantization as Q
     g = torch.Generator().manual_seed(9001)
     K, N = 1024, 520
     w = torch.randn(K, N, generator=g) * 0.05
     blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
     pre = mo.prepack_ggml_q4_0(blocks)
-    wd = mo.dequantize_ggml_q4_0(blocks, torch.float32).cpu()
-    for M, kernel, extra in ((1, "gemv", 0), (1, "gemv", _cabi.FLAG_DECODE_TMEM), (6, "gemv", 0), (14, "gemv", 0),
-                             (70, "gemm", 0), (400, "gemm", 0), (400, "gemm", _cabi.FLAG_GEMM_PAIR)):
+    wd = orc.dequantize_q4_0(blocks.cpu(), torch.float32)
+    for M, kernel, extra in ((1, "gemv", 0), (6, "gemv", 0), (14, "gemv", 0), (70, "gemm", 0), (400, "gemm", 0)):
         x = torch.randn(M, K, generator=g).half()
         lin = x.float() @ wd
         for flag, ref in ((_cabi.FLAG_ACT_SILU, torch.nn.functional.silu(lin)),

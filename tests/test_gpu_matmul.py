@@ -231,49 +231,6 @@ def test_config5_gemm_sweep(mo, cuda_dev, M):
 
 
 @pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 4096), (4096, 11008), (1056, 200), (96, 16)])
-def test_decode_tensor_memory_kernel(mo, cuda_dev, K, N, xdtype):
-    """M = 1 on the tcgen05 / tensor-memory decode kernel (selected by flag): same tolerance,
-    bitwise repeatable, no bounded wait gave up.  Covers a k split across a thread-block
-    cluster, a panel with fewer than eight column tiles and an odd number of 32-k blocks."""
-    from metalops_b200 import _cabi, quantization as Q
-    w, x = make_case(4000 + K + N, 1, K, N, xdtype)
-    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
-    pre = mo.prepack_ggml_q4_0(blocks)
-    y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv", flags=_cabi.FLAG_DECODE_TMEM)
-    assert Q.wait_status(cuda_dev) == 0
-    ref = c_oracle.matmul_f32(x, blocks.cpu())
-    assert torch.isfinite(y).all()
-    assert orc.rel_l2(y, ref) <= TOL
-    y2 = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv", flags=_cabi.FLAG_DECODE_TMEM)
-    assert torch.equal(y, y2), "two runs differ bitwise"
-    # the default kernel agrees to well within the tolerance
-    y_default = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemv")
-    assert orc.rel_l2(y, y_default.float().cpu()) <= TOL
-
-
-@pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("M,K,N", [(129, 96, 48), (300, 1024, 1000), (512, 512, 512), (2048, 4096, 1024), (1000, 2080, 4112)])
-def test_prefill_cta_pair_kernel(mo, cuda_dev, M, K, N, xdtype):
-    """The cta_group::2 prefill kernel (selected by flag): same tolerance, bitwise repeatable, no
-    bounded wait gave up.  Covers row and column tails, a second CTA whose column half lies wholly
-    beyond N, an odd number of 32-k blocks and several tiles per CTA pair."""
-    from metalops_b200 import _cabi, quantization as Q
-    w, x = make_case(5000 + M + K + N, M, K, N, xdtype)
-    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
-    pre = mo.prepack_ggml_q4_0(blocks)
-    y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm", flags=_cabi.FLAG_GEMM_PAIR)
-    assert Q.wait_status(cuda_dev) == 0
-    ref = c_oracle.matmul_f32(x, blocks.cpu())
-    assert torch.isfinite(y).all()
-    assert orc.rel_l2(y, ref) <= TOL
-    y2 = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm", flags=_cabi.FLAG_GEMM_PAIR)
-    assert torch.equal(y, y2), "two runs differ bitwise"
-    y_default = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm")
-    assert orc.rel_l2(y, y_default.float().cpu()) <= TOL
-
-
-@pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,K,N", [(17, 512, 128), (33, 96, 48), (64, 4096, 1000), (100, 1056, 200), (128, 2048, 4112),
                                    (20, 4096, 4096), (128, 11008, 4096)])
 def test_small_batch_tensor_memory_kernel(mo, cuda_dev, M, K, N, xdtype):
