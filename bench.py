@@ -7,7 +7,9 @@ Headline workload (N = 1): the Llama-2-7B-shaped decode projections at M = 1 —
 q/k/v/o [4096 -> 4096], gate/up [4096 -> 11008], down [11008 -> 4096], all with distinct q4_0
 weights (3.64 GB of packed weights, 29x the L2), fp16 activations.  One step = one pass over all
 224 projections.  The metric is algorithmic GB/s: (18 bytes per 32 weights + X + Y bytes) / time.
-The same run also reports the prefill GEMM (M = 2048, K = 4096, N = 14336, bf16) in TFLOP/s.
+The same line also carries the prefill GEMM (M = 2048, K = 4096, N = 14336, bf16) in TFLOP/s, the
+packer's throughput, the M sweeps of the other configurations and, on several GPUs, the sharded
+70B-shaped layers with and without their collectives.
 
 Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement of the
 reference's own torch path (dequantise + matmul) on the host cores instead.
@@ -15,7 +17,9 @@ reference's own torch path (dequantise + matmul) on the host cores instead.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -32,6 +36,7 @@ LAYERS = 32
 PROJ = [("q", 4096, 4096), ("k", 4096, 4096), ("v", 4096, 4096), ("o", 4096, 4096),
         ("gate", 4096, 11008), ("up", 4096, 11008), ("down", 11008, 4096)]
 GEMM_SHAPE = (2048, 4096, 14336)          # M, K, N of the prefill configuration
+SHARD_SHAPES = [("gate_up", 8192, 28672), ("down", 28672, 8192)]     # Llama-3-70B-shaped layers
 
 
 def gemv_bytes(M: int, K: int, N: int) -> int:
@@ -50,15 +55,22 @@ def measured_peaks():
 
 
 def recorded_traffic():
-    """DRAM traffic figures taken from the committed ncu summaries (dram__bytes_read.sum +
-    dram__bytes_write.sum of one captured launch; the bench never runs under a profiler).
+    """DRAM traffic of one captured launch (dram__bytes_read.sum + dram__bytes_write.sum), constants
+    recorded from profiler captures of small cases; the bench itself never runs under a profiler.
+    decode: DRAM bytes per algorithmic byte of the persistent single-row kernel;
+    gemm: bytes of one M=2048, K=4096, N=14336 launch."""
+    return {"decode_dram_bytes_per_algorithmic_byte": 1.00, "gemm_dram_bytes_per_launch": 62.1e6}
 
-    gemv: profiles/gemv_m1_kernel_llama7b_layer.md — DRAM bytes / algorithmic bytes measured on the
-    three shapes of a layer (1.002, 1.000, 1.001), i.e. traffic grows in proportion to the bytes
-    of a launch; the step's average launch is scaled by that ratio.
-    gemm: profiles/gemm_tcgen05_kernel_m2048.md — 50.0 MB read + 12.1 MB written for the bench's
-    M=2048, K=4096, N=14336 launch."""
-    return {"gemv_dram_bytes_per_algorithmic_byte": 1.001, "gemm_dram_bytes_per_launch": 62.1e6}
+
+def cpu_model() -> str:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for ln in f:
+                if ln.lower().startswith("model name"):
+                    return ln.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 class ClockSampler:
@@ -114,6 +126,16 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def keep_busy(clk: ClockSampler, elapsed_ms: float, work, sync, seconds: float = 0.6) -> None:
+    """Keeps the same work running a little longer when the timed region was too short for the
+    100 ms clock sampler to have seen it."""
+    if clk.proc is not None and elapsed_ms < 400:
+        t_end = time.time() + seconds
+        while time.time() < t_end:
+            work()
+        sync()
+
+
 # ------------------------------------------------------------------------------------------
 # reference arm / CPU baseline: the torch restatement of the reference's CPU path
 # ------------------------------------------------------------------------------------------
@@ -138,6 +160,15 @@ def cpu_layer_pass(items) -> float:
     return time.perf_counter() - t0
 
 
+def cpu_matmul_only_pass(items_dense) -> float:
+    """The same seven products on weights dequantised beforehand (fp32): what the reference's path
+    would cost if the dequantisation were free."""
+    t0 = time.perf_counter()
+    for x, w in items_dense:
+        torch.matmul(x, w)
+    return time.perf_counter() - t0
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -159,10 +190,28 @@ def run_reference(args) -> None:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "llama2-7b decode projections, M=1, q4_0 weights, fp16 activations", "m": M,
                    "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "cpu": cpu_model(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def cpu_baseline():
+    from oracle import q4_0_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    items = cpu_layer_inputs(1002, 1)
+    cpu_layer_pass(items)
+    best = min(cpu_layer_pass(items) for _ in range(3))
+    dense = [(x.float(), orc.dequantize_q4_0(b, torch.float32)) for x, b in items]
+    cpu_matmul_only_pass(dense)
+    best_mm = min(cpu_matmul_only_pass(dense) for _ in range(3))
+    layer_bytes = sum(gemv_bytes(1, K, N) for _, K, N in PROJ)
+    return {"value": layer_bytes / best / 1e9, "unit": "GB/s", "cores": cores, "cpu": cpu_model(), "kind": "port",
+            "sample": "one layer (7 projections, 1/32 of a step) through the CPU restatement of the reference's "
+                      "dequantise + torch matmul path, best of 3", "seconds": best,
+            "matmul_only": {"value": layer_bytes / best_mm / 1e9, "unit": "GB/s (same algorithmic bytes)", "seconds": best_mm,
+                            "note": "fp32 matmul on weights dequantised beforehand: the floor of the reference's path"}}
 
 
 # ------------------------------------------------------------------------------------------
@@ -184,6 +233,61 @@ def build_stack(dev, layers: int, seed: int):
     return stack
 
 
+def build_chains(dev, stack, xs, layers):
+    """The step as stage lists of the persistent kernel, four stages per layer (q|k|v, o, gate|up,
+    down).  `ready`: every stage reads an input that is ready when the launch starts, the situation
+    of the per-projection launches it replaces.  `dataflow`: each stage is fed by an earlier stage's
+    output (q|k|v <- previous down, o <- v, gate|up <- o, down <- gate), scaled to unit variance."""
+    from metalops_b200 import decode as D
+    n_out = sum(N + (-N) % 8 for _, _, N, _ in stack)
+    ready = D.DecodeChain(torch.float16, dev, out_capacity=n_out)
+    flow = D.DecodeChain(torch.float16, dev, out_capacity=n_out)
+    a4, a11 = 1.0 / (0.02 * math.sqrt(4096)), 1.0 / (0.02 * math.sqrt(11008))
+    prev = xs[4096].view(-1)
+    for layer in range(layers):
+        q, k, v, o, ga, up, dn = [p for *_, p in stack[7 * layer: 7 * layer + 7]]
+        ready.add_stage(xs[4096].view(-1), [q, k, v])
+        ready.add_stage(xs[4096].view(-1), [o])
+        ready.add_stage(xs[4096].view(-1), [ga, up])
+        ready.add_stage(xs[11008].view(-1), [dn])
+        s0 = flow.add_stage(prev, [q, k, v], alphas=[a4] * 3)
+        s1 = flow.add_stage((s0, 2), [o], alphas=[a4])
+        s2 = flow.add_stage((s1, 0), [ga, up], alphas=[a4] * 2)
+        s3 = flow.add_stage((s2, 0), [dn], alphas=[a11])
+        prev = (s3, 0)
+    return ready.build(), flow.build()
+
+
+def time_steps(stream, step, steps: int, warmup: int, clk_index=None, dist_barrier=None):
+    """W warm-up steps, then exactly `steps` steps between two events on `stream` (plus one event
+    per step for the median); returns (total ms, per-step ms list, clock summary or None)."""
+    for _ in range(warmup):
+        step()
+    stream.synchronize()
+    if dist_barrier is not None:
+        dist_barrier()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    clocks = None
+
+    def timed():
+        evs[0].record(stream)
+        for i in range(steps):
+            step()
+            evs[i + 1].record(stream)
+        stream.synchronize()
+
+    if clk_index is not None:
+        with ClockSampler(clk_index) as clk:
+            timed()
+            keep_busy(clk, evs[0].elapsed_time(evs[-1]), step, stream.synchronize)
+        clocks = clk.summary()
+    else:
+        timed()
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return evs[0].elapsed_time(evs[-1]), per, clocks
+
+
 def run_ours(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -194,188 +298,263 @@ def run_ours(args) -> None:
     torch.cuda.set_device(dev)
     import torch.distributed as dist
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+    barrier = dist.barrier if world > 1 else None
 
     from metalops_b200 import _cabi
     from metalops_b200 import quantization as Q
     lib = _cabi.load()
     _cabi.stream_ptr(dev)
 
-    M = args.m
-    flags = 0 if args.no_pdl else _cabi.FLAG_PDL
-    # weak scaling: every rank owns the column shard [rank*N, (rank+1)*N) of layers that are
-    # `world` times wider; per-GPU shapes (and bytes) are those of the 7B stack.
+    M = 1
+    # On several GPUs every rank runs its own copy of the step on its own weights: independent
+    # replicas with no communication (the sharded layers with their collectives are the `sharded`
+    # object below).
     stack = build_stack(dev, args.layers, 1002 + rank)
-    xs = {K: torch.randn(M, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
-    ys = [torch.empty(M, N, device=dev, dtype=torch.float16) for _, _, N, _ in stack]
+    xs = {K: torch.randn(1, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
     step_bytes = sum(gemv_bytes(M, K, N) for _, K, N, _ in stack)
-    launches_per_step = len(stack)
-
+    packed_bytes = sum(p.nbytes() for *_, p in stack)
+    n_proj = len(stack)
     stream = torch.cuda.Stream(dev)
+    peaks = measured_peaks()
+    traffic = recorded_traffic()
 
-    def enqueue_step():
-        sp = torch.cuda.current_stream(dev).cuda_stream
-        for (name, K, N, pre), y in zip(stack, ys):
-            x = xs[K]
-            rc = lib.q4b_gemv(x.data_ptr(), _cabi.F16, M, K, pre.data.data_ptr(), K, N, y.data_ptr(), N, flags, sp)
-            if rc:
-                _cabi.check(rc, "q4b_gemv")
-
-    graph = None
     with torch.cuda.stream(stream):
-        for _ in range(2):
-            enqueue_step()
-        stream.synchronize()
-        if not args.no_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                enqueue_step()
+        chain_ready, chain_flow = build_chains(dev, stack, xs, args.layers)
 
-        def step():
-            if graph is not None:
-                graph.replay()
-            else:
-                enqueue_step()
-
-        for _ in range(args.warmup):
-            step()
-        stream.synchronize()
+        # ---- headline: the 224 projections as one persistent launch, inputs ready at launch ----
+        ms, per, clocks = time_steps(stream, chain_ready.run, args.steps, args.warmup, clk_index=local, dist_barrier=barrier)
+        if Q.wait_status(dev) != 0:
+            raise SystemExit("a bounded device-side wait gave up")
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local) as clk:
-            e0.record(stream)
-            for _ in range(args.steps):
-                step()
-            e1.record(stream)
-            stream.synchronize()
-            if clk.proc is not None and e0.elapsed_time(e1) < 400:
-                # keep the same work running a little longer so the sampler sees clocks under load
-                t_end = time.time() + 0.6
-                while time.time() < t_end:
-                    step()
-                stream.synchronize()
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-        ms = e0.elapsed_time(e1)
-
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     value = step_bytes * world * args.steps / (ms * 1e-3) / 1e9
     per_gpu = step_bytes * args.steps / (ms * 1e-3) / 1e9
-    peaks = measured_peaks()
-    traffic = recorded_traffic()
 
-    # ---- end to end through the C ABI with host buffers (H2D of X, product, D2H of Y) ------
+    extras = {}
+    with torch.cuda.stream(stream):
+        # ---- the same step with every stage fed by an earlier stage's output ----
+        ms_f, per_f, _ = time_steps(stream, chain_flow.run, max(5, min(args.steps, 50)), 3)
+        nf = len(per_f)
+        extras["dataflow"] = {"gbps": step_bytes * nf / (ms_f * 1e-3) / 1e9, "frac": step_bytes * nf / (ms_f * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                              "ms_per_step": ms_f / nf,
+                              "note": "each stage reads the output of an earlier stage (q|k|v <- down, o <- v, gate|up <- o, "
+                                      "down <- gate), handed over inside the kernel"}
+        # ---- and as 224 separate launches (q4b_gemv, CUDA graph + programmatic dependent launch) ----
+        ys = [torch.empty(1, N, device=dev, dtype=torch.float16) for _, _, N, _ in stack]
+
+        def enqueue_launches():
+            sp = torch.cuda.current_stream(dev).cuda_stream
+            for (name, K, N, pre), y in zip(stack, ys):
+                rc = lib.q4b_gemv(xs[K].data_ptr(), _cabi.F16, 1, K, pre.data.data_ptr(), K, N, y.data_ptr(), N, _cabi.FLAG_PDL, sp)
+                if rc:
+                    _cabi.check(rc, "q4b_gemv")
+
+        enqueue_launches()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            enqueue_launches()
+        ms_l, per_l, _ = time_steps(stream, graph.replay, max(5, min(args.steps, 50)), 3)
+        nl = len(per_l)
+        extras["per_projection_launches"] = {"gbps": step_bytes * nl / (ms_l * 1e-3) / 1e9,
+                                             "frac": step_bytes * nl / (ms_l * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                             "ms_per_step": ms_l / nl, "launches_per_step": n_proj,
+                                             "note": "q4b_gemv per projection, CUDA graph + programmatic dependent launch"}
+        del graph
+
+    # ---- end to end through the public API with host buffers ------------------------------
     e2e = None
     if not args.skip_e2e:
-        hx = {K: torch.randn(M, K, dtype=torch.float16).pin_memory() for K in (4096, 11008)}
-        hy = [torch.empty(M, N, dtype=torch.float16).pin_memory() for _, _, N, _ in stack]
-        dx = {K: torch.empty(M, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
+        e2e = bench_e2e(dev, stream, lib, stack, xs, chain_ready, step_bytes, world, args, barrier)
 
-        def e2e_step():
-            sp = stream.cuda_stream
-            for (name, K, N, pre), y, yh in zip(stack, ys, hy):
-                rc = lib.q4b_matmul_host(hx[K].data_ptr(), dx[K].data_ptr(), _cabi.F16, M, pre.data.data_ptr(), K, N,
-                                         y.data_ptr(), yh.data_ptr(), 0, sp)
-                if rc:
-                    _cabi.check(rc, "q4b_matmul_host")
-            stream.synchronize()
-
-        with torch.cuda.stream(stream):
-            for _ in range(min(3, args.warmup)):
-                e2e_step()
-            if world > 1:
-                dist.barrier()
-            n_e2e = max(3, min(args.steps, 20))
-            t0 = time.perf_counter()
-            for _ in range(n_e2e):
-                e2e_step()
-            dt = time.perf_counter() - t0
-        te = torch.tensor([dt], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e = {"value": step_bytes * world * n_e2e / float(te.item()) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": sum(2 * M * K for _, K, _, _ in stack),
-               "d2h_bytes_per_step": sum(2 * M * N for _, _, N, _ in stack), "steps": n_e2e,
-               "note": "per projection: H2D of X from pinned memory, kernel, D2H of Y, through q4b_matmul_host"}
-
-    # ---- prefill GEMM (rank 0's GPU only at N > 1: the same kernel runs on every rank) -----
-    gemm = None
-    batch = None
+    gemm = quant = sweeps = batch = sharded = None
     if not args.skip_gemm:
-        gemm = bench_gemm(dev, stream, lib, peaks, traffic, args)
-        if rank == 0 and args.layers >= 4:
-            batch = bench_batch(dev, stream, lib, stack, flags)
+        gemm = bench_gemm(dev, stream, lib, peaks, traffic, local)
+    if rank == 0 and not args.skip_extra:
+        quant = bench_quantize(dev, stream, peaks)
+        if args.layers >= 4:
+            batch = bench_batch(dev, stream, lib, stack)
+    del chain_ready, chain_flow, stack
+    torch.cuda.empty_cache()
+    if rank == 0 and not args.skip_extra:
+        sweeps = bench_sweeps(dev, stream, lib, peaks)
+    if not args.skip_extra:
+        sharded = bench_sharded(dev, stream, lib, rank, world, peaks)
 
     out = None
     if rank == 0:
-        clocks = clk.summary()
+        frac = per_gpu / peaks["hbm_gbs"]
         out = {
             "metric": "q4_0_gemv_gbps_m1", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "ms_per_step_median": statistics.median(per),
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"llama2-7b decode projections, M={M}, q4_0 weights, fp16 activations",
-                       "layers": args.layers, "projections_per_step": launches_per_step,
-                       "packed_weight_bytes_per_gpu": sum(p.nbytes() for *_, p in stack),
+                       "layers": args.layers, "projections_per_step": n_proj,
+                       "packed_weight_bytes_per_gpu": packed_bytes,
                        "l2": "inputs (3.6 GB of distinct weights per step) exceed the 126 MB L2; no flush needed",
-                       "launch": ("cuda graph" if graph is not None else "stream") + (", pdl" if flags else ""),
-                       "parallelism": f"column-parallel x{world}, outputs kept sharded (no collective in the step)"},
+                       "launch": "one persistent launch per step over a stage list (4 stages per layer: q|k|v, o, gate|up, "
+                                 "down); every stage's input is ready when the launch starts, as for the per-projection "
+                                 "launches it replaces; value = bytes of the 224 projections / step time, unchanged",
+                       "parallelism": ("one GPU" if world == 1 else
+                                       f"{world} independent replicas of the step, one per GPU, no communication "
+                                       "(see `sharded` for the sharded layers and their collectives)")},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": per_gpu / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                         "frac": frac, "peak_source": peaks["source"],
                          "frac_of_nominal_8tbs": per_gpu / 8000.0,
-                         "kernel": "gemv_m1_kernel", "launches": launches_per_step * args.steps,
-                         "avg_launch_us": ms * 1e3 / (launches_per_step * args.steps),
-                         "traffic": (traffic.get("gemv_dram_bytes_per_algorithmic_byte") or 0) * step_bytes / launches_per_step
-                         if traffic.get("gemv_dram_bytes_per_algorithmic_byte") else None},
-            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+                         "kernel": "chain_kernel", "launches": args.steps,
+                         "avg_launch_us": ms * 1e3 / args.steps,
+                         "traffic": traffic["decode_dram_bytes_per_algorithmic_byte"] * step_bytes,
+                         "traffic_source": "constant recorded from a profiler capture of a small case, scaled by bytes"},
+            "decode_variants": extras,
+            "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
         }
-        if gemm is not None:
-            out["gemm"] = gemm
-        if batch is not None:
-            out["decode_batch"] = batch
-    if rank == 0 and not args.skip_cpu and world >= 1:
-        out["cpu_baseline"] = cpu_baseline()
-    if rank == 0:
+        for key, val in (("gemm", gemm), ("quantize", quant), ("sweeps", sweeps), ("decode_batch", batch), ("sharded", sharded)):
+            if val is not None:
+                out[key] = val
+        if not args.skip_cpu:
+            if world == 1:
+                out["cpu_baseline"] = cpu_baseline()
+            else:
+                out["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "cpu": cpu_model(), "kind": "port",
+                                       "sample": "not timed while the other ranks' processes share the host cores; "
+                                                 "see the reference arm (--impl reference)"}
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def cpu_baseline():
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    items = cpu_layer_inputs(1002, 1)
-    cpu_layer_pass(items)
-    best = min(cpu_layer_pass(items) for _ in range(3))
-    layer_bytes = sum(gemv_bytes(1, K, N) for _, K, N in PROJ)
-    return {"value": layer_bytes / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": "one layer (7 projections, 1/32 of a step) through the CPU restatement of the reference's "
-                      "dequantise + torch matmul path, best of 3", "seconds": best}
-
-
-def bench_gemm(dev, stream, lib, peaks, traffic, args):
+def bench_e2e(dev, stream, lib, stack, xs, chain, step_bytes, world, args, barrier):
+    """The step through the public API with HOST buffers: copy the inputs from pinned memory, run the
+    stage list, copy all 224 outputs back, wait.  Also the older per-projection form
+    (q4b_matmul_host: H2D of X, product, D2H of Y for every projection)."""
     from metalops_b200 import _cabi
+    import torch.distributed as dist
+    hx = {K: torch.randn(1, K, dtype=torch.float16).pin_memory() for K in (4096, 11008)}
+    used = chain._out_used
+    hy = torch.empty(used, dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        for K in (4096, 11008):
+            xs[K].copy_(hx[K], non_blocking=True)
+        chain.run()
+        hy.copy_(chain.out_flat[:used], non_blocking=True)
+        stream.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            e2e_step()
+        if barrier is not None:
+            barrier()
+        n = max(3, min(args.steps, 50))
+        t0 = time.perf_counter()
+        for _ in range(n):
+            e2e_step()
+        dt = time.perf_counter() - t0
+    te = torch.tensor([dt], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    out = {"value": step_bytes * world * n / float(te.item()) / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": 2 * (4096 + 11008), "d2h_bytes_per_step": 2 * used, "steps": n,
+           "note": "per step: H2D of the input rows from pinned memory, one persistent launch, D2H of all 224 outputs, "
+                   "stream synchronised; host wall clock"}
+    # per-projection host calls (the reference's API shape: one matmul call per projection)
+    ys = [torch.empty(1, N, device=dev, dtype=torch.float16) for _, _, N, _ in stack]
+    hys = [torch.empty(1, N, dtype=torch.float16).pin_memory() for _, _, N, _ in stack]
+    dx = {K: torch.empty(1, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
+
+    def per_call_step():
+        sp = stream.cuda_stream
+        for (name, K, N, pre), y, yh in zip(stack, ys, hys):
+            rc = lib.q4b_matmul_host(hx[K].data_ptr(), dx[K].data_ptr(), _cabi.F16, 1, pre.data.data_ptr(), K, N,
+                                     y.data_ptr(), yh.data_ptr(), 0, sp)
+            if rc:
+                _cabi.check(rc, "q4b_matmul_host")
+        stream.synchronize()
+
+    with torch.cuda.stream(stream):
+        per_call_step()
+        n2 = max(3, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for _ in range(n2):
+            per_call_step()
+        dt2 = time.perf_counter() - t0
+    out["per_projection_calls"] = {"value": step_bytes * n2 / dt2 / 1e9, "unit": "GB/s (this rank)",
+                                   "h2d_bytes_per_step": sum(2 * K for _, K, _, _ in stack),
+                                   "d2h_bytes_per_step": sum(2 * N for _, _, N, _ in stack),
+                                   "note": "q4b_matmul_host per projection: H2D of X, kernel, D2H of Y"}
+    return out
+
+
+def distinct_weights(dev, K, N, min_total_bytes, seed, outliers=False, std=0.02):
+    """Enough distinct q4_0 weights of one shape to exceed L2 when rotated."""
     from metalops_b200 import quantization as Q
-    M, K, N = GEMM_SHAPE
-    g = torch.Generator(device=dev).manual_seed(1003)
-    # several distinct weights and activations so consecutive launches do not hit in L2
-    nset = 4
-    pres, xs, ys = [], [], []
-    for _ in range(nset):
-        w = torch.randn(K, N, generator=g, device=dev) * 0.02
-        idx = torch.randint(0, K * N, (K * N // 1000,), generator=g, device=dev)
-        w.view(-1)[idx] = torch.where(torch.rand(idx.numel(), generator=g, device=dev) < 0.5, -0.5, 0.5)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    one = K * N // 32 * 18
+    n = max(2, -(-min_total_bytes // one))
+    pres = []
+    for _ in range(n):
+        w = torch.randn(K, N, generator=g, device=dev) * std
+        if outliers:
+            idx = torch.randint(0, K * N, (K * N // 1000,), generator=g, device=dev)
+            w.view(-1)[idx] = torch.where(torch.rand(idx.numel(), generator=g, device=dev) < 0.5, -0.5, 0.5)
         pres.append(Q._quantize_impl(w, False, True)[1])
-        xs.append(torch.randn(M, K, generator=g, device=dev).bfloat16())
-        ys.append(torch.empty(M, N, device=dev, dtype=torch.bfloat16))
         del w
-    reps = 20
+    return pres
+
+
+def time_launches(stream, enqueue, reps, graph=True):
+    """Average device time (ms) of one of `reps` launches enqueued by `enqueue(i)`, replayed as a
+    CUDA graph when it can be captured."""
+    with torch.cuda.stream(stream):
+        for i in range(min(reps, 4)):
+            enqueue(i)
+        stream.synchronize()
+        g = None
+        if graph:
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(reps):
+                        enqueue(i)
+            except Exception:
+                g = None
+                torch.cuda.synchronize()
+
+        def run():
+            if g is not None:
+                g.replay()
+            else:
+                for i in range(reps):
+                    enqueue(i)
+
+        run()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        run()
+        e1.record(stream)
+        stream.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def bench_gemm(dev, stream, lib, peaks, traffic, local):
+    """Prefill GEMM of configuration 3 (M=2048, K=4096, N=14336, bf16): a 20-launch burst and a run of
+    more than a second, each with its own clock samples."""
+    from metalops_b200 import _cabi
+    M, K, N = GEMM_SHAPE
+    pres = distinct_weights(dev, K, N, 4 * K * N // 32 * 18, 1003, outliers=True)
+    g = torch.Generator(device=dev).manual_seed(1003)
+    xs = [torch.randn(M, K, generator=g, device=dev).bfloat16() for _ in pres]
+    ys = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in pres]
+    nset = len(pres)
 
     def run(n):
         sp = stream.cuda_stream
@@ -385,34 +564,111 @@ def bench_gemm(dev, stream, lib, peaks, traffic, args):
             if rc:
                 _cabi.check(rc, "q4b_gemm")
 
+    flop = 2.0 * M * K * N
     with torch.cuda.stream(stream):
         run(5)
         stream.synchronize()
-        detail = torch.zeros(1, dtype=torch.int32)
-        import ctypes
         d = ctypes.c_int(0)
-        rc = lib.q4b_wait_status(stream.cuda_stream, ctypes.byref(d))
-        if rc:
-            return {"error": f"gemm status {rc} detail {d.value}"}
+        if lib.q4b_wait_status(stream.cuda_stream, ctypes.byref(d)):
+            return {"error": f"gemm wait status detail {d.value}"}
+        reps = 20
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        run(reps)
-        e1.record(stream)
-        stream.synchronize()
-    ms = e0.elapsed_time(e1) / reps
-    tf = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+        with ClockSampler(local) as clk:
+            e0.record(stream)
+            run(reps)
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        # sustained: keep launching for well over a second
+        n_long = max(200, int(1500.0 / ms))
+        with ClockSampler(local) as clk2:
+            e0.record(stream)
+            run(n_long)
+            e1.record(stream)
+            stream.synchronize()
+        ms_long = e0.elapsed_time(e1) / n_long
+    tf, tf_long = flop / (ms * 1e-3) / 1e12, flop / (ms_long * 1e-3) / 1e12
     return {"metric": "q4_0_gemm_tflops_m2048", "value": tf, "unit": "TFLOP/s", "ms_per_launch": ms,
             "config": {"workload": f"prefill GEMM M={M} K={K} N={N}, bf16 activations, q4_0 weights with 0.1% outliers",
-                       "l2": f"{nset} distinct weight/activation sets (4 x 150 MB) rotate, larger than L2"},
+                       "l2": f"{nset} distinct weight/activation sets rotate, larger than L2"},
             "dtype": "bf16",
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": tf / peaks["bf16_tflops"], "frac_of_sustained": tf / peaks["bf16_tflops_sustained"],
-                         "frac_of_nominal_2250": tf / 2250.0, "peak_source": peaks["source"],
-                         "kernel": "gemm_tcgen05_kernel", "traffic": traffic.get("gemm_dram_bytes_per_launch")},
-            "gpu_launches": reps}
+                         "frac": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0, "peak_source": peaks["source"],
+                         "kernel": "gemm_tcgen05_kernel", "traffic": traffic.get("gemm_dram_bytes_per_launch"),
+                         "note": f"{reps}-launch burst against the burst cuBLAS figure"},
+            "clocks": clk.summary(),
+            "sustained": {"value": tf_long, "unit": "TFLOP/s", "launches": n_long, "seconds": ms_long * n_long / 1e3,
+                          "frac_of_sustained_peak": tf_long / peaks["bf16_tflops_sustained"], "clocks": clk2.summary()},
+            "gpu_launches": reps + n_long}
 
 
-def bench_batch(dev, stream, lib, stack, flags):
+def bench_quantize(dev, stream, peaks):
+    """Configuration 5's packer: fp16 [N=14336, K=4096] (nn.Linear layout, read in place) with 1% of
+    the blocks all zero -> q4_0 blocks, and the same with both output forms."""
+    from metalops_b200 import quantization as Q
+    K, N = 4096, 14336
+    g = torch.Generator(device=dev).manual_seed(1005)
+    ws = []
+    for _ in range(3):                                     # 3 x 117 MB of inputs rotate: larger than L2
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).half()
+        mask = torch.rand(N, K // 32, generator=g, device=dev) < 0.01
+        w.view(N, K // 32, 32)[mask] = 0
+        ws.append(w)
+    algo = K * N * 2 + K * N // 32 * 18
+    out = {"bytes_per_launch": algo, "config": "fp16 [14336, 4096] nn.Linear layout, 1% all-zero blocks"}
+    for label, want_blocks, want_pre in (("blocks_only", True, False), ("blocks_and_streaming_layout", True, True)):
+        with torch.cuda.stream(stream):
+            for w in ws:
+                Q._quantize_impl(w.t(), want_blocks, want_pre)
+            stream.synchronize()
+            reps = 12
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(reps):
+                Q._quantize_impl(ws[i % 3].t(), want_blocks, want_pre)
+            e1.record(stream)
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        gbps = algo / us / 1e3
+        out[label] = {"us_per_launch": us, "gbps": gbps, "frac_of_hbm": gbps / peaks["hbm_gbs"],
+                      "note": "includes the allocator call for the outputs" if label == "blocks_only" else
+                              "algorithmic bytes count one output form; this writes two"}
+    return out
+
+
+def bench_sweeps(dev, stream, lib, peaks):
+    """Configuration 5's M sweep at K=4096, N=14336 and configuration 4 on one GPU (K=8192, N=28672
+    and K=28672, N=8192 at M = 1 and 128), through q4b_matmul (the dispatcher picks the kernel)."""
+    from metalops_b200 import _cabi
+    out = {}
+    cases = [("k4096_n14336", 4096, 14336, (1, 2, 8, 32, 128, 512, 4096)),
+             ("k8192_n28672", 8192, 28672, (1, 128)), ("k28672_n8192", 28672, 8192, (1, 128))]
+    for label, K, N, Ms in cases:
+        pres = distinct_weights(dev, K, N, 300 << 20, 2000 + K % 97)
+        res = {}
+        for M in Ms:
+            x = torch.randn(M, K, device=dev, dtype=torch.float16)
+            y = torch.empty(M, N, device=dev, dtype=torch.float16)
+            reps = max(len(pres), 8 if M >= 512 else 24)
+
+            def enqueue(i, x=x, y=y, M=M):
+                p = pres[i % len(pres)]
+                rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, p.data.data_ptr(), K, N, y.data_ptr(), N, _cabi.FLAG_PDL,
+                                    torch.cuda.current_stream(dev).cuda_stream)
+                if rc:
+                    _cabi.check(rc, "q4b_matmul")
+
+            ms = time_launches(stream, enqueue, reps)
+            gb, tf = gemv_bytes(M, K, N) / (ms * 1e-3) / 1e9, 2.0 * M * K * N / (ms * 1e-3) / 1e12
+            res[f"m{M}"] = {"us": ms * 1e3, "gbps": gb, "frac_of_hbm": gb / peaks["hbm_gbs"], "tflops": tf,
+                            "frac_of_bf16_burst": tf / peaks["bf16_tflops"]}
+        out[label] = res
+        del pres
+        torch.cuda.empty_cache()
+    return out
+
+
+def bench_batch(dev, stream, lib, stack):
     """Decode batches: the same projections at M = 4, 16 and 64 rows through q4b_matmul (decode kernel,
     tensor-memory kernel), the first four layers (455 MB of weights, larger than L2) in a CUDA
     graph.  Reported for information next to the M = 1 headline."""
@@ -423,30 +679,14 @@ def bench_batch(dev, stream, lib, stack, flags):
         xs = {K: torch.randn(M, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
         ys = [torch.empty(M, N, device=dev, dtype=torch.float16) for _, _, N, _ in sub]
 
-        def enqueue():
-            sp = torch.cuda.current_stream(dev).cuda_stream
-            for (name, K, N, pre), y in zip(sub, ys):
-                rc = lib.q4b_matmul(xs[K].data_ptr(), _cabi.F16, M, K, pre.data.data_ptr(), K, N, y.data_ptr(), N, flags, sp)
-                if rc:
-                    _cabi.check(rc, "q4b_matmul")
+        def enqueue(i, xs=xs, ys=ys, M=M):
+            name, K, N, pre = sub[i]
+            rc = lib.q4b_matmul(xs[K].data_ptr(), _cabi.F16, M, K, pre.data.data_ptr(), K, N, ys[i].data_ptr(), N, _cabi.FLAG_PDL,
+                                torch.cuda.current_stream(dev).cuda_stream)
+            if rc:
+                _cabi.check(rc, "q4b_matmul")
 
-        with torch.cuda.stream(stream):
-            enqueue()
-            stream.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                enqueue()
-            for _ in range(3):
-                g.replay()
-            stream.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 20
-            e0.record(stream)
-            for _ in range(reps):
-                g.replay()
-            e1.record(stream)
-            stream.synchronize()
-        ms = e0.elapsed_time(e1) / reps
+        ms = time_launches(stream, enqueue, len(sub)) * len(sub)
         nbytes = sum(gemv_bytes(M, K, N) for _, K, N, _ in sub)
         flops = sum(2.0 * M * K * N for _, K, N, _ in sub)
         out[f"m{M}"] = {"gbps": nbytes / (ms * 1e-3) / 1e9, "tflops": flops / (ms * 1e-3) / 1e12,
@@ -454,14 +694,134 @@ def bench_batch(dev, stream, lib, stack, flags):
     return out
 
 
-def run_probe(spec: str) -> None:
-    """`--probe MxKxN`: six distinct weights, one q4b_matmul launch each (fp16 activations), then the
-    wait status; prints the average device time.  A small fixed case for profiler captures."""
+def bench_sharded(dev, stream, lib, rank, world, peaks):
+    """Configuration 4: the Llama-3-70B-shaped layers (K=8192, N=28672 and K=28672, N=8192, M = 1 and
+    128, fp16) sharded over the ranks, strong scaling: total work is fixed, every rank holds 1/world
+    of each weight.  Column-parallel over N: local product alone, with the NCCL all-gather of the
+    outputs, and (M = 1) with the gather fused into the kernel's stores to peer memory.  Row-parallel
+    over K for the down shape: NCCL all-reduce of fp32 partials, and (M = 1) the fused peer-store
+    reduction.  Times are device times, the maximum over ranks; throughputs are whole-job."""
+    import torch.distributed as dist
     from metalops_b200 import _cabi
     from metalops_b200 import quantization as Q
-    M, K, N = (int(v) for v in spec.lower().split("x"))
+    from metalops_b200 import sharding as S
+    res = {"world": world, "scaling": "strong",
+           "note": "algorithmic bytes / flops of the WHOLE layer over the slowest rank's device time; `local` runs as a CUDA "
+                   "graph, the variants with a collective are enqueued call by call from Python (host-driven)"}
+
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def whole_job(M, K, N, ms):
+        gb = gemv_bytes(M, K, N) / (ms * 1e-3) / 1e9
+        tf = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+        return {"us": ms * 1e3, "gbps": gb, "frac_of_hbm_x_world": gb / (peaks["hbm_gbs"] * world), "tflops": tf}
+
+    for label, K, N in SHARD_SHAPES:
+        entry = {}
+        # ---- column-parallel: rank r holds columns [r*N/world, (r+1)*N/world) ----
+        n_loc = N // world
+        pres = distinct_weights(dev, K, n_loc, 300 << 20, 3000 + rank)
+        for M in (1, 128):
+            x = torch.randn(M, K, device=dev, dtype=torch.float16)
+            y = torch.empty(M, n_loc, device=dev, dtype=torch.float16)
+            full = torch.empty(world * M, n_loc, device=dev, dtype=torch.float16)
+            reps = max(len(pres), 16)
+
+            def local(i, x=x, y=y, M=M):
+                p = pres[i % len(pres)]
+                rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, p.data.data_ptr(), K, n_loc, y.data_ptr(), n_loc, 0,
+                                    torch.cuda.current_stream(dev).cuda_stream)
+                if rc:
+                    _cabi.check(rc, "q4b_matmul")
+
+            def with_gather(i, x=x, y=y, M=M, full=full):
+                local(i)
+                if world > 1:
+                    dist.all_gather_into_tensor(full, y)
+
+            e = {"local": whole_job(M, K, N, max_over_ranks(time_launches(stream, local, reps)))}
+            if world > 1:
+                dist.barrier()
+                e["nccl_all_gather"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, with_gather, reps, graph=False)))
+                if M == 1:
+                    try:
+                        fused = S.FusedGatherBuffer(N, rank, world, torch.float16, dev)
+
+                        def fused_step(i, x=x, fused=fused):
+                            fused.gemv(x, pres[i % len(pres)])
+                        dist.barrier()
+                        e["fused_peer_store_gather"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, fused_step, reps, graph=False)))
+                    except Exception as ex:           # symmetric memory unavailable on this box
+                        e["fused_peer_store_gather"] = {"error": str(ex)[:200]}
+            entry[f"column_parallel_m{M}"] = e
+        del pres
+        torch.cuda.empty_cache()
+        # ---- row-parallel over K (the down projection after a column-parallel gate|up) ----
+        if label == "down":
+            k_loc = K // world
+            pres = distinct_weights(dev, k_loc, N, 300 << 20, 4000 + rank)
+            for M in (1, 128):
+                x = torch.randn(M, k_loc, device=dev, dtype=torch.float16)
+                y = torch.empty(M, N, device=dev, dtype=torch.float16)
+                acc = torch.empty(M, N, device=dev, dtype=torch.float32)
+                reps = max(len(pres), 16)
+
+                def partial(i, x=x, y=y, M=M):
+                    p = pres[i % len(pres)]
+                    rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, k_loc, p.data.data_ptr(), k_loc, N, y.data_ptr(), N, 0,
+                                        torch.cuda.current_stream(dev).cuda_stream)
+                    if rc:
+                        _cabi.check(rc, "q4b_matmul")
+
+                def with_reduce(i, y=y, acc=acc):
+                    partial(i)
+                    if world > 1:
+                        acc.copy_(y)
+                        dist.all_reduce(acc)
+
+                e = {"local": whole_job(M, K, N, max_over_ranks(time_launches(stream, partial, reps)))}
+                if world > 1:
+                    dist.barrier()
+                    e["nccl_all_reduce_fp32"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, with_reduce, reps, graph=False)))
+                entry[f"row_parallel_m{M}"] = e
+            del pres
+            torch.cuda.empty_cache()
+        res[label] = entry
+    if world > 1:
+        res["limit"] = ("at M = 1 a rank's product takes a few microseconds, so the step is bounded by the collective's latency "
+                        "(NCCL launch + ring/tree steps, or two symmetric-memory barriers for the fused form), not by HBM")
+    return res
+
+
+def run_probe(spec: str) -> None:
+    """`--probe MxKxN`: six distinct weights, one q4b_matmul launch each (fp16 activations), then the
+    wait status; prints the average device time.  `--probe chain:L`: L layers of the 7B-shaped stage
+    list, three runs.  Small fixed cases for profiler captures."""
+    from metalops_b200 import _cabi
+    from metalops_b200 import quantization as Q
     dev = torch.device("cuda", 0)
     lib = _cabi.load()
+    if spec.startswith("chain:"):
+        layers = int(spec.split(":")[1])
+        stack = build_stack(dev, layers, 4242)
+        xs = {K: torch.randn(1, K, device=dev, dtype=torch.float16) for K in (4096, 11008)}
+        ready, flow = build_chains(dev, stack, xs, layers)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ready.run()
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(3):
+            ready.run()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        print(json.dumps({"probe": spec, "launches": 3, "us_per_launch": e0.elapsed_time(e1) * 1e3 / 3,
+                          "bytes_per_launch": sum(gemv_bytes(1, K, N) for _, K, N, _ in stack), "wait_status": Q.wait_status(dev)}))
+        return
+    M, K, N = (int(v) for v in spec.lower().split("x"))
     g = torch.Generator(device=dev).manual_seed(4242)
     pres = [Q._quantize_impl(torch.randn(K, N, generator=g, device=dev) * 0.02, False, True)[1] for _ in range(6)]
     x = torch.randn(M, K, generator=g, device=dev).half()
@@ -481,17 +841,15 @@ def run_probe(spec: str) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--m", type=int, default=1, help="decode batch rows (1..16)")
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--no-pdl", action="store_true")
-    ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--probe", default=None, metavar="MxKxN", help="run one small product six times and exit (profiler captures)")
+    ap.add_argument("--probe", default=None, metavar="MxKxN|chain:L", help="run one small case and exit (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-gemm", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-extra", action="store_true", help="skip the packer, sweep, batch and sharded objects")
     args = ap.parse_args()
     if args.probe:
         run_probe(args.probe)

@@ -180,6 +180,31 @@ Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
                              int64_t K, int64_t N, int64_t group, float *addend_out, void *stream);
 
 /*
+ * Weights from other GGML tools, and the reference's group-wise INT8 weights.
+ *
+ * q4b_import_ggml    block_q4_0 data as those tools store it: rows of K/32 blocks per output
+ *                    feature, [N, K/32, 18], byte j of a block = value j | value (j + 16) << 4 (the
+ *                    order the reference's own helper reads, quant_kernels.metal:1714-1731; format
+ *                    provenance quantization.py:292-304)  ->  this library's blocks [K/32, N, 18].
+ * q4b_quantize_ggml  quantizes with those tools' scale rule instead of the reference's amax / 7:
+ *                    d = (value of largest magnitude in the block) / -8, q = clamp(round(w / d) + 8,
+ *                    0, 15), all-zero block: d = 0, q = 8; fp32 arithmetic, ties to even.  Writes
+ *                    blocks (required) and optionally the streaming layout.  The matmul kernels
+ *                    accept either rule (negative d included).
+ * q4b_int8g_matmul   Y = X . ((w_q - zero) * scale) for int8 w_q [K, N] and scales / zeros
+ *                    [ceil(K/group), N] of dtype sz_dtype: matmul_int8 of the reference
+ *                    (quantization.py:242-286, quant_kernels.metal:40-109, core_mps.mm:4516-4574).
+ *                    fp32 accumulation on the CUDA cores, X and Y f16 or bf16; any M (tiled eight
+ *                    rows at a time), w_int8 4-byte aligned.
+ */
+Q4B_API int q4b_import_ggml(const void *raw, int64_t K, int64_t N, void *blocks_out, void *stream);
+Q4B_API int q4b_quantize_ggml(const void *w, int w_dtype, int64_t K, int64_t N, int layout,
+                              void *blocks_out, void *prepacked_out, void *stream);
+Q4B_API int q4b_int8g_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *w_int8,
+                             const void *scales, const void *zeros, int sz_dtype, int64_t K, int64_t N,
+                             int64_t group, void *y, int64_t ldy, void *stream);
+
+/*
  * Single-row decode (M = 1) over a list of stages in ONE persistent launch (no reference
  * counterpart: the reference launches its 64x32-tile kernel once per product,
  * core_mps.mm:5917-5975, quant_kernels.metal:1738-1886).

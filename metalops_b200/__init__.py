@@ -19,6 +19,7 @@ from .quantization import (  # noqa: E402
     dequantize_int4,
     matmul_ggml_q4_0,
     fused_rmsnorm_linear_int4,
+    import_ggml_q4_0,
     matmul_int4,
     matmul_int4_gelu,
     matmul_int4_silu,
@@ -30,7 +31,8 @@ from .quantization import (  # noqa: E402
     rmsnorm,
     unpack_ggml_q4_0,
 )
-from .sharding import ColumnParallelQ4Linear, RowParallelQ4Linear, shard_bounds  # noqa: E402
+from .decode import DecodeChain, matmul_ggml_q4_0_grouped  # noqa: E402
+from .sharding import ColumnParallelQ4Linear, FusedGatherBuffer, RowParallelQ4Linear, shard_bounds  # noqa: E402
 
 __version__ = "0.1.0"
 
@@ -46,6 +48,6 @@ __all__ = [
     "quantize_ggml_q4_0", "dequantize_ggml_q4_0", "matmul_ggml_q4_0", "prepack_ggml_q4_0",
     "unpack_ggml_q4_0", "Q4Prepacked", "Int4Linear", "Q4Linear", "prepack_int4", "quantize_int4", "dequantize_int4", "matmul_int4", "matmul_int4_silu", "matmul_int4_gelu",
     "fused_rmsnorm_linear_int4", "rmsnorm",
-    "matmul_int8", "ColumnParallelQ4Linear", "RowParallelQ4Linear", "shard_bounds", "has_native_kernels", "QK4_0",
+    "matmul_int8", "import_ggml_q4_0", "DecodeChain", "matmul_ggml_q4_0_grouped", "FusedGatherBuffer", "ColumnParallelQ4Linear", "RowParallelQ4Linear", "shard_bounds", "has_native_kernels", "QK4_0",
     "BLOCK_Q4_0_SIZE",
 ]

@@ -53,6 +53,9 @@ SYMBOLS = {
     "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
     "q4b_gemv_gather": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _vp]),
+    "q4b_import_ggml": (_ci, [_vp, _i64, _i64, _vp, _vp]),
+    "q4b_quantize_ggml": (_ci, [_vp, _ci, _i64, _i64, _ci, _vp, _vp, _vp]),
+    "q4b_int8g_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),
     "q4b_gemv_grouped": (_ci, [_vp, _ci, _i64, ctypes.POINTER(ChainProduct), _ci, _ci, _vp]),
     "q4b_chain_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(ChainStage), _ci]),
     "q4b_chain_build": (_ci, [ctypes.POINTER(ChainStage), _ci, _vp, ctypes.c_size_t, _vp]),

@@ -108,7 +108,7 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], uint32_t a0, uint32_t a1, 
 
 // What the weight producer and the work split need of a stage, copied to shared memory when the
 // kernel starts (the full Stage stays in global memory: inputs, outputs, epilogue parameters).
-struct Compact {
+struct alignas(16) Compact {
     int32_t nblk;               // K / 32
     int32_t base, extra, off;   // tiles per worker, workers with one more, first worker (see worker_tiles)
     const uint8_t *w[MAX_PRODUCTS];
@@ -234,46 +234,73 @@ chain_kernel(const Stage *__restrict__ stages, const Compact *__restrict__ ctab,
             const int nblk = cs.nblk, nblk_pad = (((nblk + 1) >> 1) + 1) / 2 * 4;
             const uint32_t xq_s = xq_base + (uint32_t)b * xbuf_bytes, xs_s = xq_s + (uint32_t)cap_blocks * 64u;
 #pragma unroll 1
-            for (int blk = lw * 32 + lane; blk < nblk_pad; blk += LOADER_WARPS * 32) {
+            for (int base = lw * 32; base < nblk_pad; base += LOADER_WARPS * 32) {     // warp-uniform trip count
+                const int blk = base + lane;
                 uint32_t w[16];                                      // 32 fp16 / bf16 values, two per word
                 uint32_t w2[16];
-                if (blk >= nblk) {
+                if (xp != nullptr || blk >= nblk) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) w[i] = 0u;
-                } else if (xp != nullptr) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(xp + (size_t)blk * QK);
+                    if (blk < nblk) {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(xp + (size_t)blk * QK);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint4 v = __ldcg(src + i);
-                        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                        for (int i = 0; i < 4; ++i) {
+                            const uint4 v = __ldcg(src + i);
+                            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                        }
                     }
-                } else {
-                    // hand-over words (two values, epoch) of an earlier stage: poll until all sixteen carry
-                    // this launch's epoch
-                    auto poll = [&](const unsigned long long *src, uint32_t (&d)[16]) {
-                        long long t_start = 0;
-                        for (int it = 0;; ++it) {
-                            uint32_t ok = 1u;
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                uint32_t f0, f1;
-                                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                             : "=r"(d[2 * i]), "=r"(f0), "=r"(d[2 * i + 1]), "=r"(f1)
-                                             : "l"(src + (size_t)blk * 16 + 2 * i) : "memory");
+                }
+                if (xp == nullptr) {
+                    // Hand-over words (two values, epoch) of an earlier stage.  A block's 32 values come
+                    // from two column tiles, written by two warps.  While waiting, every lane looks only at
+                    // the two words where they meet (the last of one, the first of the other): polling all
+                    // sixteen from every SM saturates L2 and slows the very stores it waits for.  Once all
+                    // lanes of the warp see this launch's epoch there, the sixteen words are read and every
+                    // flag is checked.  The warp stays converged, so the conversion below runs once.
+                    const bool mine = blk < nblk;
+                    const unsigned long long *ba = lla + (size_t)blk * 16, *bb = llb + (size_t)blk * 16;
+                    long long t_start = 0;
+                    for (int it = 0;; ++it) {
+                        uint32_t ok = 1u, f0, f1, t0, t1;
+                        if (mine) {
+                            asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(t0), "=r"(f0) : "l"(ba + 7) : "memory");
+                            asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(t1), "=r"(f1) : "l"(ba + 8) : "memory");
+                            ok = (f0 == epoch && f1 == epoch) ? 1u : 0u;
+                            if (xform == 1) {
+                                asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(t0), "=r"(f0) : "l"(bb + 7) : "memory");
+                                asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(t1), "=r"(f1) : "l"(bb + 8) : "memory");
                                 ok &= (f0 == epoch && f1 == epoch) ? 1u : 0u;
                             }
-                            if (ok) break;
-                            __nanosleep(100);
-                            if ((it & 15) == 15) {
-                                if (aborted() || other_cta_aborted()) { *(volatile int *)&sh.abort = 1; break; }
-                                const long long now = clock64();
-                                if (t_start == 0) t_start = now;
-                                else if (now - t_start > WAIT_LIMIT_CYCLES) { give_up(501); break; }
-                            }
                         }
-                    };
-                    poll(lla, w);
-                    if (xform == 1) poll(llb, w2);
+                        if (__all_sync(0xffffffffu, ok != 0u)) {
+                            if (mine) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                                 : "=r"(w[2 * i]), "=r"(f0), "=r"(w[2 * i + 1]), "=r"(f1) : "l"(ba + 2 * i) : "memory");
+                                    ok &= (f0 == epoch && f1 == epoch) ? 1u : 0u;
+                                }
+                                if (xform == 1) {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) {
+                                        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                                     : "=r"(w2[2 * i]), "=r"(f0), "=r"(w2[2 * i + 1]), "=r"(f1) : "l"(bb + 2 * i) : "memory");
+                                        ok &= (f0 == epoch && f1 == epoch) ? 1u : 0u;
+                                    }
+                                }
+                            }
+                            if (__all_sync(0xffffffffu, ok != 0u)) break;
+                        }
+                        __nanosleep(150);
+                        bool stop = false;
+                        if ((it & 15) == 15) {
+                            if (aborted() || other_cta_aborted()) { *(volatile int *)&sh.abort = 1; stop = true; }
+                            const long long now = clock64();
+                            if (t_start == 0) t_start = now;
+                            else if (now - t_start > WAIT_LIMIT_CYCLES) { give_up(501); stop = true; }
+                        }
+                        if (__any_sync(0xffffffffu, stop)) break;
+                    }
                 }
                 float f[32];
 #pragma unroll
@@ -318,6 +345,7 @@ chain_kernel(const Stage *__restrict__ stages, const Compact *__restrict__ ctab,
                     hi[2 * c] = bytes1(e[0], e[4], e[1], e[5]);
                     hi[2 * c + 1] = bytes1(e[2], e[6], e[3], e[7]);
                 }
+                if (blk >= nblk_pad) continue;
                 const uint32_t dst = xq_s + (uint32_t)blk * 64u;
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16), "r"(lo[4]), "r"(lo[5]), "r"(lo[6]), "r"(lo[7]) : "memory");
@@ -574,7 +602,7 @@ static int check_stage(const q4b_chain_stage &s, int index) {
     if (s.xform != Q4B_CHAIN_X_PLAIN && s.xform != Q4B_CHAIN_X_SILU_MUL) return Q4B_ERR_ARG;
     if (s.x != nullptr) {
         if (s.xform != Q4B_CHAIN_X_PLAIN) return Q4B_ERR_ARG;
-        if (!aligned(s.x, 8)) return Q4B_ERR_ALIGN;
+        if (!aligned(s.x, 16)) return Q4B_ERR_ALIGN;
     } else {
         if (s.x_stage < 0 || s.x_stage >= index || s.x_product < 0) return Q4B_ERR_ARG;
         if (s.xform == Q4B_CHAIN_X_SILU_MUL && (s.x_stage2 < 0 || s.x_stage2 >= index || s.x_product2 < 0)) return Q4B_ERR_ARG;

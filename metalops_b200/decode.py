@@ -85,7 +85,9 @@ class DecodeChain:
     every :meth:`run`.  Runs of one chain must not overlap on the GPU.
     """
 
-    def __init__(self, dtype: torch.dtype, device: torch.device):
+    def __init__(self, dtype: torch.dtype, device: torch.device, out_capacity: Optional[int] = None):
+        """``out_capacity`` (elements): carve all outputs out of one flat buffer (``out_flat``) of
+        that many elements, so that a caller can copy every result to the host in one transfer."""
         if dtype not in (torch.float16, torch.bfloat16):
             raise RuntimeError("chain dtype must be fp16 or bf16")
         self.dtype, self.device = dtype, torch.device(device)
@@ -94,7 +96,8 @@ class DecodeChain:
         self._stages: List[dict] = []
         self.outputs: List[List[torch.Tensor]] = []
         self._workspace: Optional[torch.Tensor] = None
-        self._keep: list = []
+        self.out_flat = torch.empty(out_capacity, dtype=dtype, device=self.device) if out_capacity else None
+        self._out_used = 0
 
     def add_stage(self, x, weights: Sequence[Union[torch.Tensor, Q4Prepacked]], *, alphas=None, addends=None, acts=None,
                   xform: Optional[str] = None) -> int:
@@ -129,7 +132,16 @@ class DecodeChain:
                 if self._stages[src[0]]["pres"][src[1]].N != K:
                     raise RuntimeError("the earlier output's length is not this stage's K")
         self._stages.append(st)
-        self.outputs.append([torch.empty(p.N, dtype=self.dtype, device=self.device) for p in pres])
+        outs = []
+        for p in pres:
+            if self.out_flat is None:
+                outs.append(torch.empty(p.N, dtype=self.dtype, device=self.device))
+            else:
+                if self._out_used + p.N > self.out_flat.numel():
+                    raise RuntimeError("out_capacity is too small for the outputs of the stages added")
+                outs.append(self.out_flat[self._out_used:self._out_used + p.N])
+                self._out_used += p.N + (-p.N) % 8          # keep every output 16-byte aligned
+        self.outputs.append(outs)
         self._workspace = None
         return index
 

@@ -92,16 +92,47 @@ def _quantize_impl(weight: torch.Tensor, want_blocks: bool, want_prepacked: bool
     return blocks, (Q4Prepacked(pre, K, N) if pre is not None else None)
 
 
-def quantize_ggml_q4_0(weight: torch.Tensor) -> torch.Tensor:
+def quantize_ggml_q4_0(weight: torch.Tensor, scale_mode: str = "metalcore") -> torch.Tensor:
     """Quantize ``weight [K, N]`` to GGML block_q4_0: returns uint8 ``[K/32, N, 18]``.
 
     Bit-identical to the reference (quantization.py:307-371) for fp32, fp16 and bf16 weights.
     Note the reference's docstring says ``[num_blocks, 18]``; its code and this function return
     ``[K/32, N, 18]``.
-    """
-    blocks, pre = _quantize_impl(weight, True, True)
+
+    ``scale_mode="ggml"`` (not in the reference) uses the scale rule of other GGML tools instead of
+    the reference's ``amax / 7``: ``d = (value of largest magnitude) / -8``,
+    ``q = clamp(round(w / d) + 8, 0, 15)``, an all-zero block gets ``d = 0, q = 8``."""
+    if scale_mode == "metalcore":
+        blocks, pre = _quantize_impl(weight, True, True)
+    elif scale_mode == "ggml":
+        blocks, pre = _quantize_ggml_rule(weight)
+    else:
+        raise ValueError(f"scale_mode must be 'metalcore' or 'ggml', not {scale_mode!r}")
     blocks._q4b_prepacked = (_version_of(blocks), pre)
     return blocks
+
+
+def _quantize_ggml_rule(weight: torch.Tensor):
+    if weight.dim() != 2:
+        raise ValueError("weight must be 2-D [K, N]")
+    _cabi.require_device(weight, "weight")
+    if weight.dtype not in _cabi.DTYPE_CODE:
+        raise RuntimeError(f"unsupported weight dtype {weight.dtype}")
+    K, N = weight.shape
+    assert K % QK4_0 == 0, f"K ({K}) must be divisible by {QK4_0}"
+    if weight.is_contiguous():
+        layout, src = _cabi.LAYOUT_KN, weight
+    elif weight.t().is_contiguous():
+        layout, src = _cabi.LAYOUT_NK, weight.t()
+    else:
+        layout, src = _cabi.LAYOUT_KN, weight.contiguous()
+    blocks = torch.empty((K // QK4_0, N, BLOCK_Q4_0_SIZE), dtype=torch.uint8, device=weight.device)
+    pre = _alloc_prepacked(K, N, weight.device)
+    with torch.cuda.device(weight.device):
+        rc = _cabi.load().q4b_quantize_ggml(src.data_ptr(), _cabi.DTYPE_CODE[src.dtype], K, N, layout, blocks.data_ptr(),
+                                            pre.data_ptr(), _cabi.stream_ptr(weight.device))
+    _cabi.check(rc, "quantize_ggml_q4_0")
+    return blocks, Q4Prepacked(pre, K, N)
 
 
 def prepack_ggml_q4_0(W_blocks: torch.Tensor) -> Q4Prepacked:
@@ -401,10 +432,53 @@ def fused_rmsnorm_linear_int4(X: torch.Tensor, W_norm: torch.Tensor, W_packed: t
     return matmul_int4(rmsnorm(X, W_norm, eps), W_packed, scales, zeros, group_size)
 
 
-def matmul_int8(X, W_packed, scales, zeros, group_size: int = 128):
-    """INT8 group-wise matmul of the reference (quantization.py:242-286): not part of the INT4
-    path; no sm_100a kernel is built for it and there is no CPU fallback."""
-    raise NotImplementedError("matmul_int8 has no sm_100a kernel in this build (and no fallback by design)")
+def matmul_int8(X: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
+                group_size: int = 128) -> torch.Tensor:
+    """``Y = X @ ((W_packed - zero) * scale)`` for int8 ``W_packed [K, N]`` and per-group
+    ``scales`` / ``zeros [ceil(K/group_size), N]`` — quantization.py:242-286 (its Metal kernel:
+    quant_kernels.metal:40-109).  fp32 accumulation, one rounding to ``X.dtype``; fp32 ``X`` is
+    computed through fp16 like the other entry points."""
+    _cabi.require_device(X, "X")
+    _cabi.require_device(W_packed, "W_packed")
+    if X.dim() != 2 or W_packed.dim() != 2 or W_packed.dtype != torch.int8:
+        raise RuntimeError("X must be [M, K] and W_packed int8 [K, N]")
+    K, N = W_packed.shape
+    ng = (K + group_size - 1) // group_size
+    if X.shape[1] != K or tuple(scales.shape) != (ng, N) or tuple(zeros.shape) != (ng, N) or scales.dtype != zeros.dtype:
+        raise RuntimeError(f"shapes: X [M, {K}], scales and zeros [{ng}, {N}] of one dtype")
+    if scales.dtype not in _cabi.DTYPE_CODE:
+        raise RuntimeError(f"unsupported scales dtype {scales.dtype}")
+    in_dtype = X.dtype
+    x = X.half() if in_dtype == torch.float32 else X
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"X must be float16, bfloat16 or float32 (got {in_dtype})")
+    x, w, s, z = x.contiguous(), W_packed.contiguous(), scales.contiguous(), zeros.contiguous()
+    M = x.shape[0]
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return y.to(in_dtype)
+    with torch.cuda.device(x.device):
+        rc = _cabi.load().q4b_int8g_matmul(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), w.data_ptr(), s.data_ptr(),
+                                           z.data_ptr(), _cabi.DTYPE_CODE[s.dtype], K, N, group_size, y.data_ptr(), y.stride(0),
+                                           _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "matmul_int8")
+    return y.float() if in_dtype == torch.float32 else y
+
+
+def import_ggml_q4_0(raw: torch.Tensor) -> torch.Tensor:
+    """block_q4_0 data as other GGML tools store it — uint8 ``[N, K/32, 18]``, rows of blocks per
+    output feature, byte j of a block = value j | value (j + 16) << 4 — converted to this package's
+    ``[K/32, N, 18]`` (interleaved nibbles), ready for :func:`matmul_ggml_q4_0`."""
+    _cabi.require_device(raw, "raw")
+    if raw.dtype != torch.uint8 or raw.dim() != 3 or raw.shape[2] != BLOCK_Q4_0_SIZE:
+        raise RuntimeError("raw must be uint8 [N, K/32, 18]")
+    r = raw.contiguous()
+    N, nb = r.shape[0], r.shape[1]
+    blocks = torch.empty((nb, N, BLOCK_Q4_0_SIZE), dtype=torch.uint8, device=r.device)
+    with torch.cuda.device(r.device):
+        rc = _cabi.load().q4b_import_ggml(r.data_ptr(), nb * QK4_0, N, blocks.data_ptr(), _cabi.stream_ptr(r.device))
+    _cabi.check(rc, "import_ggml_q4_0")
+    return blocks
 
 
 class Int4Linear(nn.Module):

@@ -64,7 +64,6 @@ class ColumnParallelQ4Linear(nn.Module):
         self._matmul = matmul or Q.matmul_ggml_q4_0
         self.register_buffer("weight_blocks", torch.zeros((K // Q.QK4_0, self.n1 - self.n0, Q.BLOCK_Q4_0_SIZE),
                                                           dtype=torch.uint8))
-        self._prepacked = None
 
     @classmethod
     def from_float(cls, weight_kn: torch.Tensor, rank: int, world: int, group=None, matmul=None,
@@ -114,6 +113,41 @@ class ColumnParallelQ4Linear(nn.Module):
         _cabi.check(rc, "q4b_gemv_gather")
         self._gather_hdl.barrier()                      # every rank's stores have landed
         return self._gather_buf[:M]
+
+
+class FusedGatherBuffer:
+    """The gathered output ``[max_rows, N]`` of a column-parallel decode product in symmetric memory
+    (peer-mapped on every rank), and the launch that fills it: each rank's decode kernel stores its
+    ``[M, N/g]`` columns into every rank's buffer over NVLink (plain peer stores), with a
+    symmetric-memory barrier on the stream before (nobody still reads the previous result) and after
+    (every rank's stores have landed).  Takes the weight per call, so one buffer serves many layers
+    of the same width."""
+
+    def __init__(self, N: int, rank: int, world: int, dtype: torch.dtype, device, group=None, max_rows: int = 16):
+        import torch.distributed._symmetric_memory as symm_mem
+        if N % world:
+            raise RuntimeError("fused gather needs N divisible by the number of ranks")
+        self.N, self.rank, self.world, self.n0 = N, rank, world, rank * (N // world)
+        group = group if group is not None else dist.group.WORLD
+        self.buf = symm_mem.empty((max_rows, N), dtype=dtype, device=device)
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+
+    def gemv(self, x: torch.Tensor, pre: "Q.Q4Prepacked") -> torch.Tensor:
+        import ctypes
+        from . import _cabi
+        M = x.shape[0]
+        if M > self.buf.shape[0] or M > 16 or x.dtype != self.buf.dtype or pre.N != self.N // self.world:
+            raise RuntimeError("fused gather: up to 16 rows of the buffer's dtype, weight shard of N / world columns")
+        xc = x.contiguous()
+        self.hdl.barrier()
+        ptrs = (ctypes.c_void_p * self.world)(*self.ptrs)
+        with torch.cuda.device(xc.device):
+            rc = _cabi.load().q4b_gemv_gather(xc.data_ptr(), _cabi.DTYPE_CODE[xc.dtype], M, xc.stride(0), pre.data.data_ptr(),
+                                              pre.K, pre.N, ptrs, self.world, self.n0, self.N, 0, _cabi.stream_ptr(xc.device))
+        _cabi.check(rc, "q4b_gemv_gather")
+        self.hdl.barrier()
+        return self.buf[:M]
 
 
 class RowParallelQ4Linear(nn.Module):

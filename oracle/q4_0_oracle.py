@@ -144,3 +144,68 @@ def dequantize_int4_groupwise(packed, scales, zeros, group_size: int = 128, dtyp
     q[1::2] = (packed >> 4).float()
     gi = torch.arange(K) // group_size
     return ((q - zeros[gi]) * scales[gi]).to(dtype)
+
+
+# ---------------------------------------------------------------------------------------
+# Group-wise INT8 weights (quantization.py:242-286): w_q int8 [K, N], scales / zeros
+# [ceil(K/group), N]; W = (w_q - zero) * scale, Y = X @ W.
+# ---------------------------------------------------------------------------------------
+
+def dequantize_int8_groupwise(w_q: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """fp32 W of the loop at quantization.py:277-284 (before its cast to X.dtype)."""
+    gi = torch.arange(w_q.shape[0]) // group_size
+    return (w_q.float() - zeros.float()[gi]) * scales.float()[gi]
+
+
+def matmul_int8_fp32(X: torch.Tensor, w_q, scales, zeros, group_size: int = 128) -> torch.Tensor:
+    return X.float() @ dequantize_int8_groupwise(w_q, scales, zeros, group_size)
+
+
+# ---------------------------------------------------------------------------------------
+# GGML-tool conventions (format provenance: quantization.py:292-304).  Scale rule as the build's
+# configuration 1 states it: d = (value of largest magnitude) / -8, q = clamp(round(w / d) + 8, 0, 15);
+# an all-zero block has d = 0 and q = 8.  fp32 arithmetic, ties to even (torch.round), the first
+# value wins among equal magnitudes.  Original storage order (the one the reference's helper at
+# quant_kernels.metal:1714-1731 reads): rows of K/32 blocks per output feature, byte j of a block =
+# value j | value (j + 16) << 4.
+# ---------------------------------------------------------------------------------------
+
+def quantize_q4_0_ggml_rule(weight: torch.Tensor) -> torch.Tensor:
+    """[K, N] -> uint8 [K/32, N, 18] in this build's (interleaved-nibble) layout."""
+    K, N = weight.shape
+    nb = K // QK
+    w = weight.float().view(nb, QK, N)
+    idx = w.abs().argmax(dim=1, keepdim=True)                 # first index of the maximum
+    vmax = torch.gather(w, 1, idx)                            # [nb, 1, N]
+    d = torch.where(vmax == 0, torch.zeros_like(vmax), vmax / -8.0)     # +0 for an all-zero block
+    safe = torch.where(d == 0, torch.ones_like(d), d)
+    q = torch.where(d == 0, torch.full_like(w, 8.0), ((w / safe).round() + 8.0).clamp(0, 15))
+    q = q.to(torch.uint8).permute(0, 2, 1).contiguous()       # [nb, N, 32]
+    out = torch.zeros((nb, N, BLOCK_BYTES), dtype=torch.uint8)
+    out[:, :, 0:2] = d.squeeze(1).to(torch.float16).contiguous().view(torch.uint8).view(nb, N, 2)
+    out[:, :, 2:] = q[:, :, 0::2] | (q[:, :, 1::2] << 4)
+    return out
+
+
+def ggml_split_half_from_blocks(blocks: torch.Tensor) -> torch.Tensor:
+    """This build's [K/32, N, 18] -> the original storage [N, K/32, 18] (byte j = v[j] | v[j+16] << 4)."""
+    nb, N, _ = blocks.shape
+    qs = blocks[:, :, 2:]
+    v = torch.empty((nb, N, QK), dtype=torch.uint8)
+    v[:, :, 0::2] = qs & 0x0F
+    v[:, :, 1::2] = qs >> 4
+    raw = torch.empty((nb, N, BLOCK_BYTES), dtype=torch.uint8)
+    raw[:, :, 0:2] = blocks[:, :, 0:2]
+    raw[:, :, 2:] = v[:, :, :16] | (v[:, :, 16:] << 4)
+    return raw.permute(1, 0, 2).contiguous()
+
+
+def blocks_from_ggml_split_half(raw: torch.Tensor) -> torch.Tensor:
+    """The inverse: original storage [N, K/32, 18] -> this build's [K/32, N, 18]."""
+    N, nb, _ = raw.shape
+    qs = raw[:, :, 2:]
+    v = torch.cat([qs & 0x0F, qs >> 4], dim=2)                # values 0..15 then 16..31
+    out = torch.empty((N, nb, BLOCK_BYTES), dtype=torch.uint8)
+    out[:, :, 0:2] = raw[:, :, 0:2]
+    out[:, :, 2:] = v[:, :, 0::2] | (v[:, :, 1::2] << 4)
+    return out.permute(1, 0, 2).contiguous()

@@ -124,6 +124,26 @@ def main() -> None:
         out[f"{name}.y"] = to_np(ref.matmul_int4(x, packed, scales, zeros, gs))
     np.savez_compressed(os.path.join(HERE, "int4_groupwise.npz"), **out)
 
+    # ---- group-wise INT8 matmul (matmul_int8, CPU path) --------------------------------
+    out = {}
+    for name, seed, M, K, N, gs, dt in [
+        ("g128_h", 1501, 3, 256, 40, 128, torch.float16),
+        ("g64_b", 1502, 9, 192, 130, 64, torch.bfloat16),
+        ("g128_ragged_f", 1503, 2, 160, 7, 128, torch.float32),
+    ]:
+        g = torch.Generator().manual_seed(seed)
+        w_q = torch.randint(-128, 128, (K, N), generator=g, dtype=torch.int16).to(torch.int8)
+        ng = (K + gs - 1) // gs
+        scales = (torch.rand(ng, N, generator=g) * 0.01 + 0.001).to(dt)
+        zeros = (torch.randn(ng, N, generator=g) * 20.0).to(dt)
+        x = torch.randn(M, K, generator=g).to(dt)
+        out[f"{name}.x"] = to_np(x)
+        out[f"{name}.w_q"] = to_np(w_q)
+        out[f"{name}.scales"] = to_np(scales)
+        out[f"{name}.zeros"] = to_np(zeros)
+        out[f"{name}.y"] = to_np(ref.matmul_int8(x, w_q, scales, zeros, gs))
+    np.savez_compressed(os.path.join(HERE, "int8_groupwise.npz"), **out)
+
     # ---- Int4Linear surface ----------------------------------------------------------
     torch.manual_seed(1401)
     lin = torch.nn.Linear(256, 24, bias=True)

@@ -128,8 +128,8 @@ def test_int4_errors(mo, cuda_dev):
     p, s, zz = mo.quantize_int4(w + 1.0, 16)
     with pytest.raises(RuntimeError):
         mo.matmul_int4(torch.zeros(1, 64, device=cuda_dev, dtype=torch.float16), p, s, zz, 16)   # group % 32 != 0
-    with pytest.raises(NotImplementedError):
-        mo.matmul_int8(None, None, None, None)
+    with pytest.raises(RuntimeError):                                  # CPU tensors: no fallback
+        mo.matmul_int8(torch.zeros(1, 64), torch.zeros(64, 8, dtype=torch.int8), torch.ones(1, 8), torch.zeros(1, 8), 64)
 
 
 @pytest.mark.parametrize("M", [1, 5, 16, 40, 300])

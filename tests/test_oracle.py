@@ -117,3 +117,28 @@ def test_half_conversion_helpers_exhaustive():
         vf = float(np.float32(v))
         assert lib.q4o_f32_to_f16_bits(vf) == int(np.float32(vf).astype(np.float16).view(np.uint16))
         assert lib.q4o_f32_to_bf16_bits(vf) == int(torch.tensor(vf).bfloat16().view(torch.int16)) & 0xFFFF
+
+
+def test_int8_oracle_matches_reference_fixture():
+    z = load_golden("int8_groupwise.npz")
+    for name, gs in (("g128_h", 128), ("g64_b", 64), ("g128_ragged_f", 128)):
+        x, w_q = golden_tensor(z, f"{name}.x"), golden_tensor(z, f"{name}.w_q")
+        scales, zeros, y_ref = golden_tensor(z, f"{name}.scales"), golden_tensor(z, f"{name}.zeros"), golden_tensor(z, f"{name}.y")
+        fp32 = orc.matmul_int8_fp32(x, w_q, scales, zeros, gs)
+        assert orc.rel_l2(y_ref, fp32) <= 5e-3, name
+
+
+def test_ggml_rule_and_split_half_order():
+    """Known answers of the scale rule stated for configuration 1 and of the storage order the
+    reference's own helper reads (quant_kernels.metal:1714-1731)."""
+    w = torch.zeros(64, 2)
+    w[:32, 0] = torch.arange(32, dtype=torch.float32) - 16.0        # extreme value -16 -> d = 2
+    b = orc.quantize_q4_0_ggml_rule(w)
+    assert b[0, 0, :2].view(torch.float16).item() == 2.0
+    q = torch.stack([b[0, 0, 2:] & 0xF, b[0, 0, 2:] >> 4], dim=1).reshape(-1)
+    assert q.tolist() == [min(15, max(0, int(torch.tensor((k - 16) / 2.0).round().item()) + 8)) for k in range(32)]
+    assert b[1, 0].tolist() == [0, 0] + [0x88] * 16                  # all-zero block
+    raw = orc.ggml_split_half_from_blocks(b)
+    assert tuple(raw.shape) == (2, 2, 18)
+    assert (raw[0, 0, 2] & 0xF) == q[0] and (raw[0, 0, 2] >> 4) == q[16]
+    assert torch.equal(orc.blocks_from_ggml_split_half(raw), b)
