@@ -297,6 +297,11 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     import torch.distributed as dist
+    # Libraries write to file descriptor 1 (NCCL prints its version there); the one JSON line must
+    # be alone on stdout, so everything else goes to stderr until the line is printed.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
@@ -336,37 +341,9 @@ def run_ours(args) -> None:
     value = step_bytes * world * args.steps / (ms * 1e-3) / 1e9
     per_gpu = step_bytes * args.steps / (ms * 1e-3) / 1e9
 
-    extras = {}
-    with torch.cuda.stream(stream):
-        # ---- the same step with every stage fed by an earlier stage's output ----
-        ms_f, per_f, _ = time_steps(stream, chain_flow.run, max(5, min(args.steps, 50)), 3)
-        nf = len(per_f)
-        extras["dataflow"] = {"gbps": step_bytes * nf / (ms_f * 1e-3) / 1e9, "frac": step_bytes * nf / (ms_f * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                              "ms_per_step": ms_f / nf,
-                              "note": "each stage reads the output of an earlier stage (q|k|v <- down, o <- v, gate|up <- o, "
-                                      "down <- gate), handed over inside the kernel"}
-        # ---- and as 224 separate launches (q4b_gemv, CUDA graph + programmatic dependent launch) ----
-        ys = [torch.empty(1, N, device=dev, dtype=torch.float16) for _, _, N, _ in stack]
-
-        def enqueue_launches():
-            sp = torch.cuda.current_stream(dev).cuda_stream
-            for (name, K, N, pre), y in zip(stack, ys):
-                rc = lib.q4b_gemv(xs[K].data_ptr(), _cabi.F16, 1, K, pre.data.data_ptr(), K, N, y.data_ptr(), N, _cabi.FLAG_PDL, sp)
-                if rc:
-                    _cabi.check(rc, "q4b_gemv")
-
-        enqueue_launches()
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            enqueue_launches()
-        ms_l, per_l, _ = time_steps(stream, graph.replay, max(5, min(args.steps, 50)), 3)
-        nl = len(per_l)
-        extras["per_projection_launches"] = {"gbps": step_bytes * nl / (ms_l * 1e-3) / 1e9,
-                                             "frac": step_bytes * nl / (ms_l * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                             "ms_per_step": ms_l / nl, "launches_per_step": n_proj,
-                                             "note": "q4b_gemv per projection, CUDA graph + programmatic dependent launch"}
-        del graph
+    extras = None
+    if not args.skip_variants:
+        extras = bench_variants(dev, stream, lib, stack, xs, chain_flow, step_bytes, peaks, args)
 
     # ---- end to end through the public API with host buffers ------------------------------
     e2e = None
@@ -425,10 +402,46 @@ def run_ours(args) -> None:
                 out["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "cpu": cpu_model(), "kind": "port",
                                        "sample": "not timed while the other ranks' processes share the host cores; "
                                                  "see the reference arm (--impl reference)"}
-        print(json.dumps(out))
+        os.write(json_fd, (json.dumps(out) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_variants(dev, stream, lib, stack, xs, chain_flow, step_bytes, peaks, args):
+    """The same step two other ways: with every stage fed by an earlier stage's output, and as 224
+    separate launches of the per-projection entry point."""
+    from metalops_b200 import _cabi
+    extras = {}
+    with torch.cuda.stream(stream):
+        ms_f, per_f, _ = time_steps(stream, chain_flow.run, max(5, min(args.steps, 50)), 3)
+        nf = len(per_f)
+        extras["dataflow"] = {"gbps": step_bytes * nf / (ms_f * 1e-3) / 1e9, "frac": step_bytes * nf / (ms_f * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                              "ms_per_step": ms_f / nf,
+                              "note": "each stage reads the output of an earlier stage (q|k|v <- down, o <- v, gate|up <- o, "
+                                      "down <- gate), handed over inside the kernel"}
+        ys = [torch.empty(1, N, device=dev, dtype=torch.float16) for _, _, N, _ in stack]
+
+        def enqueue_launches():
+            sp = torch.cuda.current_stream(dev).cuda_stream
+            for (name, K, N, pre), y in zip(stack, ys):
+                rc = lib.q4b_gemv(xs[K].data_ptr(), _cabi.F16, 1, K, pre.data.data_ptr(), K, N, y.data_ptr(), N, _cabi.FLAG_PDL, sp)
+                if rc:
+                    _cabi.check(rc, "q4b_gemv")
+
+        enqueue_launches()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            enqueue_launches()
+        ms_l, per_l, _ = time_steps(stream, graph.replay, max(5, min(args.steps, 50)), 3)
+        nl = len(per_l)
+        extras["per_projection_launches"] = {"gbps": step_bytes * nl / (ms_l * 1e-3) / 1e9,
+                                             "frac": step_bytes * nl / (ms_l * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                             "ms_per_step": ms_l / nl, "launches_per_step": len(stack),
+                                             "note": "q4b_gemv per projection, CUDA graph + programmatic dependent launch"}
+        del graph
+    return extras
 
 
 def bench_e2e(dev, stream, lib, stack, xs, chain, step_bytes, world, args, barrier):
@@ -574,10 +587,12 @@ def bench_gemm(dev, stream, lib, peaks, traffic, local):
         reps = 20
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clk:
+            time.sleep(0.25)                       # the sampler's first lines describe the idle GPU
             e0.record(stream)
             run(reps)
             e1.record(stream)
             stream.synchronize()
+            time.sleep(0.15)
         ms = e0.elapsed_time(e1) / reps
         # sustained: keep launching for well over a second
         n_long = max(200, int(1500.0 / ms))
@@ -605,7 +620,7 @@ def bench_gemm(dev, stream, lib, peaks, traffic, local):
 def bench_quantize(dev, stream, peaks):
     """Configuration 5's packer: fp16 [N=14336, K=4096] (nn.Linear layout, read in place) with 1% of
     the blocks all zero -> q4_0 blocks, and the same with both output forms."""
-    from metalops_b200 import quantization as Q
+    from metalops_b200 import _cabi
     K, N = 4096, 14336
     g = torch.Generator(device=dev).manual_seed(1005)
     ws = []
@@ -616,23 +631,22 @@ def bench_quantize(dev, stream, peaks):
         ws.append(w)
     algo = K * N * 2 + K * N // 32 * 18
     out = {"bytes_per_launch": algo, "config": "fp16 [14336, 4096] nn.Linear layout, 1% all-zero blocks"}
-    for label, want_blocks, want_pre in (("blocks_only", True, False), ("blocks_and_streaming_layout", True, True)):
-        with torch.cuda.stream(stream):
-            for w in ws:
-                Q._quantize_impl(w.t(), want_blocks, want_pre)
-            stream.synchronize()
-            reps = 12
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for i in range(reps):
-                Q._quantize_impl(ws[i % 3].t(), want_blocks, want_pre)
-            e1.record(stream)
-            stream.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / reps
+    lib = _cabi.load()
+    blocks = torch.empty((K // 32, N, 18), dtype=torch.uint8, device=dev)
+    pre = torch.empty(lib.q4b_prepacked_bytes(K, N), dtype=torch.uint8, device=dev)
+    for label, b_ptr, p_ptr in (("blocks_only", blocks.data_ptr(), None), ("streaming_layout_only", None, pre.data_ptr()),
+                                ("blocks_and_streaming_layout", blocks.data_ptr(), pre.data_ptr())):
+        def enqueue(i, b_ptr=b_ptr, p_ptr=p_ptr):
+            rc = lib.q4b_quantize(ws[i % 3].data_ptr(), _cabi.F16, K, N, _cabi.LAYOUT_NK, b_ptr, p_ptr,
+                                  torch.cuda.current_stream(dev).cuda_stream)
+            if rc:
+                _cabi.check(rc, "q4b_quantize")
+
+        us = time_launches(stream, enqueue, 12) * 1e3
         gbps = algo / us / 1e3
-        out[label] = {"us_per_launch": us, "gbps": gbps, "frac_of_hbm": gbps / peaks["hbm_gbs"],
-                      "note": "includes the allocator call for the outputs" if label == "blocks_only" else
-                              "algorithmic bytes count one output form; this writes two"}
+        out[label] = {"us_per_launch": us, "gbps": gbps, "frac_of_hbm": gbps / peaks["hbm_gbs"]}
+    out["note"] = ("algorithmic bytes = input + ONE 18-byte-per-block output; the last variant writes both output forms "
+                   "(1.22x the bytes) in one pass")
     return out
 
 
@@ -731,15 +745,15 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
             full = torch.empty(world * M, n_loc, device=dev, dtype=torch.float16)
             reps = max(len(pres), 16)
 
-            def local(i, x=x, y=y, M=M):
+            def local(i, x=x, y=y, M=M, pdl=_cabi.FLAG_PDL):
                 p = pres[i % len(pres)]
-                rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, p.data.data_ptr(), K, n_loc, y.data_ptr(), n_loc, 0,
+                rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, p.data.data_ptr(), K, n_loc, y.data_ptr(), n_loc, pdl,
                                     torch.cuda.current_stream(dev).cuda_stream)
                 if rc:
                     _cabi.check(rc, "q4b_matmul")
 
             def with_gather(i, x=x, y=y, M=M, full=full):
-                local(i)
+                local(i, pdl=0)
                 if world > 1:
                     dist.all_gather_into_tensor(full, y)
 
@@ -770,15 +784,15 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
                 acc = torch.empty(M, N, device=dev, dtype=torch.float32)
                 reps = max(len(pres), 16)
 
-                def partial(i, x=x, y=y, M=M):
+                def partial(i, x=x, y=y, M=M, pdl=_cabi.FLAG_PDL):
                     p = pres[i % len(pres)]
-                    rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, k_loc, p.data.data_ptr(), k_loc, N, y.data_ptr(), N, 0,
+                    rc = lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, k_loc, p.data.data_ptr(), k_loc, N, y.data_ptr(), N, pdl,
                                         torch.cuda.current_stream(dev).cuda_stream)
                     if rc:
                         _cabi.check(rc, "q4b_matmul")
 
                 def with_reduce(i, y=y, acc=acc):
-                    partial(i)
+                    partial(i, pdl=0)
                     if world > 1:
                         acc.copy_(y)
                         dist.all_reduce(acc)
@@ -849,6 +863,7 @@ def main() -> None:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-gemm", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-variants", action="store_true", help="skip the data-flow and per-projection-launch forms of the step")
     ap.add_argument("--skip-extra", action="store_true", help="skip the packer, sweep, batch and sharded objects")
     args = ap.parse_args()
     if args.probe:

@@ -165,8 +165,15 @@ Q4B_API int q4b_matmul_addend(const void *x, int x_dtype, int64_t M, int64_t ldx
  *                       (block scale d = fp16(scale), needs group % 32 == 0 and K % 32 == 0) and
  *                       writes corr [ceil(K/group), N] fp32 = 8*d - zero*scale, the per-group
  *                       constant that the symmetric tiles leave out.
- * q4b_int4g_addend      addend[m, n] = sum_g corr[g, n] * sum_{k in g} x[m, k]  (fp32 [M, N]),
- *                       to be passed to q4b_matmul_addend with the prepacked tiles.
+ *                       A scale outside fp16's range cannot be a block scale: the kernel notes it
+ *                       and q4b_int4g_prepack_status (which synchronises the stream) reports it.
+ * q4b_int4g_addend      addend[m, n] = sum_g corr[g, n] * sum_{k in g} x[m, k] + bias[n]  (fp32
+ *                       [M, N]; bias fp32 [N] or NULL), to be passed to q4b_matmul_addend with the
+ *                       prepacked tiles.  Any M.
+ * q4b_int4g_matmul_generic  the same product straight from the [K/2, N] format for the shapes the
+ *                       streaming tiles do not cover (K or group not a multiple of 32), as the
+ *                       reference's Python loop accepts them (quantization.py:207-239): fp32
+ *                       accumulation on the CUDA cores, any even K, any group.
  */
 Q4B_API int q4b_int4g_quantize(const void *w, int w_dtype, int64_t K, int64_t N, int64_t group,
                                void *packed_out, void *scales_out, void *zeros_out, void *stream);
@@ -176,8 +183,14 @@ Q4B_API int q4b_int4g_dequantize(const void *packed, const void *scales, const v
 Q4B_API int q4b_int4g_prepack(const void *packed, const void *scales, const void *zeros,
                               int sz_dtype, int64_t K, int64_t N, int64_t group,
                               void *prepacked_out, float *corr_out, void *stream);
+Q4B_API int q4b_int4g_prepack_status(void *stream, int *out_of_range);
 Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr,
-                             int64_t K, int64_t N, int64_t group, float *addend_out, void *stream);
+                             const float *bias, int64_t K, int64_t N, int64_t group, float *addend_out,
+                             void *stream);
+Q4B_API int q4b_int4g_matmul_generic(const void *x, int x_dtype, int64_t M, int64_t ldx,
+                                     const void *packed, const void *scales, const void *zeros,
+                                     int sz_dtype, int64_t K, int64_t N, int64_t group, void *y,
+                                     int64_t ldy, void *stream);
 
 /*
  * Weights from other GGML tools, and the reference's group-wise INT8 weights.
@@ -287,10 +300,16 @@ Q4B_API int q4b_rmsnorm(const void *x, int dtype, int64_t M, int64_t K, int64_t 
  * status word on the device and stop early (its output is then incomplete).  This call
  * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with
  * *detail (may be NULL) = which wait gave up (1..8 prefill kernel roles, 100-101 decode kernels,
- * 401-407 small-batch tensor-memory kernel, 500-502 persistent single-row kernel).
+ * 401-407 small-batch tensor-memory kernel, 500-504 persistent single-row kernel, 900 self-test).
  * It never traps or faults the device.
  */
 Q4B_API int q4b_wait_status(void *stream, int *detail);
+/*
+ * Launches a one-warp kernel whose bounded wait (the kernels' own wait routine, on a barrier
+ * nobody arrives at) runs out after `limit_cycles` (1 .. 2^24) and returns: q4b_wait_status then
+ * reports Q4B_ERR_TIMEOUT with detail 900.  For testing the error path; nothing faults or hangs.
+ */
+Q4B_API int q4b_selftest_wait_timeout(int64_t limit_cycles, void *stream);
 
 /*
  * Host-buffer convenience used for end-to-end timing: x_host and y_host are (ideally pinned)

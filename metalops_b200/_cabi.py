@@ -52,6 +52,7 @@ SYMBOLS = {
     "q4b_gemm": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _ci, _vp]),
     "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
+    "q4b_selftest_wait_timeout": (_ci, [_i64, _vp]),
     "q4b_gemv_gather": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _vp]),
     "q4b_import_ggml": (_ci, [_vp, _i64, _i64, _vp, _vp]),
     "q4b_quantize_ggml": (_ci, [_vp, _ci, _i64, _i64, _ci, _vp, _vp, _vp]),
@@ -69,7 +70,9 @@ SYMBOLS = {
     "q4b_int4g_quantize": (_ci, [_vp, _ci, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "q4b_int4g_dequantize": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _ci, _vp]),
     "q4b_int4g_prepack": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _vp, _vp]),
-    "q4b_int4g_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "q4b_int4g_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "q4b_int4g_prepack_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
+    "q4b_int4g_matmul_generic": (_ci, [_vp, _ci, _i64, _i64, _vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),
 }
 
 _lib = None

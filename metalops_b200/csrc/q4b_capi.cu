@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "q4b_common.cuh"
+#include "q4b_sm100_ptx.cuh"
 
 namespace q4b {
 
@@ -162,5 +163,47 @@ extern "C" int q4b_matmul_host_noalloc(const void *x_host, int x_dtype, int64_t 
     int rc = q4b_matmul(x_dev, x_dtype, M, K, prepacked, K, N, y_dev, N, Q4B_FLAG_NONE, stream);
     if (rc != Q4B_OK) return rc;
     Q4B_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, (size_t)M * N * 2, cudaMemcpyDeviceToHost, st));
+    return Q4B_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// q4b_selftest_wait_timeout: makes a bounded wait run out without harming anything.  One warp
+// initialises a shared-memory barrier that nobody will ever arrive at and waits on it with the
+// kernels' own bounded wait (ptx::mbar_wait) and a limit of `limit_cycles`; the wait gives up,
+// records code 900 and the kernel returns.  q4b_wait_status then reports Q4B_ERR_TIMEOUT / 900.
+// ---------------------------------------------------------------------------------------------
+namespace q4b {
+
+__device__ int g_selftest_status = 0;
+
+__global__ void selftest_wait_kernel(long long limit_cycles) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    ptx::mbar_wait(ptx::smem_u32(&bar), 0, &abort_flag, &g_selftest_status, 900, limit_cycles);
+}
+
+int selftest_wait_status(int *value) {
+    int h = 0;
+    Q4B_CUDA_TRY(cudaMemcpyFromSymbol(&h, g_selftest_status, sizeof(int)));
+    if (h != 0) {
+        const int zero = 0;
+        Q4B_CUDA_TRY(cudaMemcpyToSymbol(g_selftest_status, &zero, sizeof(int)));
+    }
+    *value = h;
+    return Q4B_OK;
+}
+
+}  // namespace q4b
+
+extern "C" int q4b_selftest_wait_timeout(int64_t limit_cycles, void *stream) {
+    if (limit_cycles < 1 || limit_cycles > (1LL << 24)) return Q4B_ERR_ARG;      // at most ~10 ms
+    selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)limit_cycles);
+    Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }

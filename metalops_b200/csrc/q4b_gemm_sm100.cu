@@ -496,6 +496,7 @@ int device_sm_count();
 int gemv_wait_status(int *value);
 int gemm_tmem_wait_status(int *value);
 namespace chain { int wait_status(int *value); }
+int selftest_wait_status(int *value);
 int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
                      const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
 }  // namespace q4b
@@ -562,6 +563,8 @@ extern "C" int q4b_wait_status(void *stream, int *detail) {
     if (int rc = gemm_tmem_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (int rc = chain::wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = selftest_wait_status(&hv)) return rc;
     if (h == 0) h = hv;
     if (detail) *detail = h;
     return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;

@@ -123,6 +123,10 @@ int4g_prepack_kernel(const uint8_t *__restrict__ packed, const TS *__restrict__ 
             make_uint2((uint32_t)ds[0] | ((uint32_t)ds[1] << 16), (uint32_t)ds[2] | ((uint32_t)ds[3] << 16));
 }
 
+// set when a group scale does not fit the fp16 block scale of the streaming tiles (read and cleared by
+// q4b_int4g_prepack_status)
+__device__ int g_int4g_range = 0;
+
 // corr[g, n] = 8 * fp16(scale) - zero * scale
 template <typename TS>
 __global__ void __launch_bounds__(128)
@@ -130,31 +134,38 @@ int4g_corr_kernel(const TS *__restrict__ scales, const TS *__restrict__ zeros, i
     const int64_t i = (int64_t)blockIdx.x * 128 + threadIdx.x;
     if (i >= count) return;
     const float s = Num<TS>::ld(scales + i), z = Num<TS>::ld(zeros + i);
+    if (!(fabsf(s) <= 65504.0f)) g_int4g_range = 1;            // also catches NaN
     const float d = __half2float(__float2half_rn(s));
     corr[i] = __fsub_rn(__fmul_rn(8.0f, d), __fmul_rn(z, s));
 }
 
-// addend[m, n] = sum_g corr[g, n] * (sum of x[m, k] over group g).  CTA = one row x 256 columns;
-// the group sums of the row are first built in shared memory.
+// addend[m, n] = sum_g corr[g, n] * (sum of x[m, k] over group g) (+ bias[n]).  A CTA takes whole
+// rows (grid-stride over m): the row's group sums are built once, every warp summing whole groups
+// with coalesced loads and a fixed-order shuffle reduction, then the columns are swept.
 template <typename TX>
 __global__ void __launch_bounds__(256)
-int4g_addend_kernel(const TX *__restrict__ x, int64_t ldx, const float *__restrict__ corr, int64_t K, int64_t N,
-                    int64_t group, int G, float *__restrict__ addend) {
+int4g_addend_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, const float *__restrict__ corr,
+                    const float *__restrict__ bias, int64_t K, int64_t N, int64_t group, int G, float *__restrict__ addend) {
     extern __shared__ float xs[];
-    const int64_t m = blockIdx.y;
-    const TX *xr = x + m * ldx;
-    for (int g = threadIdx.x; g < G; g += 256) {
-        const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
-        float s = 0.0f;
-        for (int64_t k = k0; k < k1; ++k) s += Num<TX>::ld(xr + k);
-        xs[g] = s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+        const TX *xr = x + m * ldx;
+        __syncthreads();
+        for (int g = warp; g < G; g += 8) {
+            const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
+            float s = 0.0f;
+            for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) xs[g] = s;
+        }
+        __syncthreads();
+        for (int64_t n = threadIdx.x; n < N; n += 256) {
+            float acc = bias != nullptr ? bias[n] : 0.0f;
+            for (int g = 0; g < G; ++g) acc = fmaf(corr[(int64_t)g * N + n], xs[g], acc);
+            addend[m * N + n] = acc;
+        }
     }
-    __syncthreads();
-    const int64_t n = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (n >= N) return;
-    float acc = 0.0f;
-    for (int g = 0; g < G; ++g) acc = fmaf(corr[(int64_t)g * N + n], xs[g], acc);
-    addend[m * N + n] = acc;
 }
 
 }  // namespace q4b
@@ -244,21 +255,33 @@ extern "C" int q4b_int4g_prepack(const void *packed, const void *scales, const v
     }
 }
 
-extern "C" int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr, int64_t K,
-                                int64_t N, int64_t group, float *addend_out, void *stream) {
+extern "C" int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr, const float *bias,
+                                int64_t K, int64_t N, int64_t group, float *addend_out, void *stream) {
     if (x == nullptr || corr == nullptr || addend_out == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || ldx < K) return Q4B_ERR_ARG;
     if (int rc = check_g(K, N, group)) return rc;
     const int64_t G = ceil_div(K, group);
-    if (G > 8192 || M > 65535) return Q4B_ERR_TOO_LARGE;
-    dim3 grid((unsigned)ceil_div(N, 256), (unsigned)M);
+    if (G > 8192) return Q4B_ERR_TOO_LARGE;
+    const unsigned grid = (unsigned)(M < 4096 ? M : 4096);
     const size_t smem = (size_t)G * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
     switch (x_dtype) {
-        case Q4B_F16: int4g_addend_kernel<__half><<<grid, 256, smem, st>>>((const __half *)x, ldx, corr, K, N, group, (int)G, addend_out); break;
-        case Q4B_BF16: int4g_addend_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>((const __nv_bfloat16 *)x, ldx, corr, K, N, group, (int)G, addend_out); break;
+        case Q4B_F16: int4g_addend_kernel<__half><<<grid, 256, smem, st>>>((const __half *)x, M, ldx, corr, bias, K, N, group, (int)G, addend_out); break;
+        case Q4B_BF16: int4g_addend_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>((const __nv_bfloat16 *)x, M, ldx, corr, bias, K, N, group, (int)G, addend_out); break;
         default: return Q4B_ERR_DTYPE;
     }
     Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_int4g_prepack_status(void *stream, int *out_of_range) {
+    Q4B_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    int h = 0;
+    Q4B_CUDA_TRY(cudaMemcpyFromSymbol(&h, g_int4g_range, sizeof(int)));
+    if (h != 0) {
+        const int zero = 0;
+        Q4B_CUDA_TRY(cudaMemcpyToSymbol(g_int4g_range, &zero, sizeof(int)));
+    }
+    if (out_of_range != nullptr) *out_of_range = h;
     return Q4B_OK;
 }

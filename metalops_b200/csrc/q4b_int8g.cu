@@ -102,7 +102,9 @@ __device__ __forceinline__ float byte_to_float(uint32_t w_xor80, int sel) {
     return __uint_as_float(__byte_perm(w_xor80, 0x4B000000u, 0x7650 | sel) & 0xFFFF00FFu | 0x4B000000u) - 8388736.0f;
 }
 
-template <typename TX, typename TS>
+// NIBBLES: wq is the group-wise INT4 format instead, uint8 [K/2, N], byte r of a column = value 2r in
+// its low and value 2r + 1 in its high nibble (values 0..15).
+template <typename TX, typename TS, bool NIBBLES>
 __global__ void __launch_bounds__(I8_THREADS)
 int8g_matmul_kernel(const TX *__restrict__ x, int M, int64_t ldx, const int8_t *__restrict__ wq, const TS *__restrict__ scales,
                     const TS *__restrict__ zeros, int64_t K, int64_t N, int group, TX *__restrict__ y, int64_t ldy) {
@@ -133,7 +135,18 @@ int8g_matmul_kernel(const TX *__restrict__ x, int M, int64_t ldx, const int8_t *
             const int64_t kk = kc + k;
             const int64_t gi = kk / group;
             float wv[4];
-            if (vec) {
+            if constexpr (NIBBLES) {
+                const uint8_t *row = reinterpret_cast<const uint8_t *>(wq) + (kk >> 1) * N;
+                const int sh = (int)(kk & 1) * 4;
+                if (vec) {
+                    const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(row + n0));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) wv[j] = (float)((word >> (8 * j + sh)) & 0xFu);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) wv[j] = n0 + j < N ? (float)((row[n0 + j] >> sh) & 0xF) : 0.0f;
+                }
+            } else if (vec) {
                 const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(wq + kk * N + n0)) ^ 0x80808080u;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) wv[j] = byte_to_float(word, j);
@@ -209,36 +222,51 @@ extern "C" int q4b_quantize_ggml(const void *w, int w_dtype, int64_t K, int64_t 
     return Q4B_OK;
 }
 
-template <typename TX, typename TS>
+template <typename TX, typename TS, bool NIBBLES>
 static int launch_int8g(const void *x, int64_t M, int64_t ldx, const void *wq, const void *scales, const void *zeros, int64_t K,
                         int64_t N, int64_t group, void *y, int64_t ldy, cudaStream_t st) {
     dim3 grid((unsigned)ceil_div(N, I8_COLS), (unsigned)ceil_div(M, I8_ROWS));
-    int8g_matmul_kernel<TX, TS><<<grid, I8_THREADS, 0, st>>>((const TX *)x, (int)M, ldx, (const int8_t *)wq, (const TS *)scales,
-                                                            (const TS *)zeros, K, N, (int)group, (TX *)y, ldy);
+    int8g_matmul_kernel<TX, TS, NIBBLES><<<grid, I8_THREADS, 0, st>>>((const TX *)x, (int)M, ldx, (const int8_t *)wq,
+                                                                     (const TS *)scales, (const TS *)zeros, K, N, (int)group,
+                                                                     (TX *)y, ldy);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
+}
+
+template <bool NIBBLES>
+static int groupwise_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *wq, const void *scales,
+                            const void *zeros, int sz_dtype, int64_t K, int64_t N, int64_t group, void *y, int64_t ldy,
+                            void *stream) {
+    if (x == nullptr || wq == nullptr || scales == nullptr || zeros == nullptr || y == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || K <= 0 || N <= 0 || group <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
+    if (NIBBLES && (K % 2)) return Q4B_ERR_SHAPE;
+    if (M > 65535LL * I8_ROWS || group > (1LL << 30)) return Q4B_ERR_TOO_LARGE;
+    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    if (!aligned(wq, 4) || !aligned(x, 2) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool xb = x_dtype == Q4B_BF16;
+    switch (sz_dtype) {
+        case Q4B_F32:
+            return xb ? launch_int8g<__nv_bfloat16, float, NIBBLES>(x, M, ldx, wq, scales, zeros, K, N, group, y, ldy, st)
+                      : launch_int8g<__half, float, NIBBLES>(x, M, ldx, wq, scales, zeros, K, N, group, y, ldy, st);
+        case Q4B_F16:
+            return xb ? launch_int8g<__nv_bfloat16, __half, NIBBLES>(x, M, ldx, wq, scales, zeros, K, N, group, y, ldy, st)
+                      : launch_int8g<__half, __half, NIBBLES>(x, M, ldx, wq, scales, zeros, K, N, group, y, ldy, st);
+        case Q4B_BF16:
+            return xb ? launch_int8g<__nv_bfloat16, __nv_bfloat16, NIBBLES>(x, M, ldx, wq, scales, zeros, K, N, group, y, ldy, st)
+                      : launch_int8g<__half, __nv_bfloat16, NIBBLES>(x, M, ldx, wq, scales, zeros, K, N, group, y, ldy, st);
+        default: return Q4B_ERR_DTYPE;
+    }
 }
 
 extern "C" int q4b_int8g_matmul(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *w_int8, const void *scales,
                                 const void *zeros, int sz_dtype, int64_t K, int64_t N, int64_t group, void *y, int64_t ldy,
                                 void *stream) {
-    if (x == nullptr || w_int8 == nullptr || scales == nullptr || zeros == nullptr || y == nullptr) return Q4B_ERR_ARG;
-    if (M < 1 || K <= 0 || N <= 0 || group <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
-    if (M > 65535LL * I8_ROWS || group > (1LL << 30)) return Q4B_ERR_TOO_LARGE;
-    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
-    if (!aligned(w_int8, 4) || !aligned(x, 2) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
-    cudaStream_t st = (cudaStream_t)stream;
-    const bool xb = x_dtype == Q4B_BF16;
-    switch (sz_dtype) {
-        case Q4B_F32:
-            return xb ? launch_int8g<__nv_bfloat16, float>(x, M, ldx, w_int8, scales, zeros, K, N, group, y, ldy, st)
-                      : launch_int8g<__half, float>(x, M, ldx, w_int8, scales, zeros, K, N, group, y, ldy, st);
-        case Q4B_F16:
-            return xb ? launch_int8g<__nv_bfloat16, __half>(x, M, ldx, w_int8, scales, zeros, K, N, group, y, ldy, st)
-                      : launch_int8g<__half, __half>(x, M, ldx, w_int8, scales, zeros, K, N, group, y, ldy, st);
-        case Q4B_BF16:
-            return xb ? launch_int8g<__nv_bfloat16, __nv_bfloat16>(x, M, ldx, w_int8, scales, zeros, K, N, group, y, ldy, st)
-                      : launch_int8g<__half, __nv_bfloat16>(x, M, ldx, w_int8, scales, zeros, K, N, group, y, ldy, st);
-        default: return Q4B_ERR_DTYPE;
-    }
+    return groupwise_matmul<false>(x, x_dtype, M, ldx, w_int8, scales, zeros, sz_dtype, K, N, group, y, ldy, stream);
+}
+
+extern "C" int q4b_int4g_matmul_generic(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *packed,
+                                        const void *scales, const void *zeros, int sz_dtype, int64_t K, int64_t N, int64_t group,
+                                        void *y, int64_t ldy, void *stream) {
+    return groupwise_matmul<true>(x, x_dtype, M, ldx, packed, scales, zeros, sz_dtype, K, N, group, y, ldy, stream);
 }

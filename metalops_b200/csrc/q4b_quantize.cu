@@ -23,6 +23,30 @@ template <> struct RoundTo<__nv_bfloat16> {
     static __device__ __forceinline__ float ld(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 };
 
+// Two values rounded to T and widened again.  The packed conversions (two floats -> half2 / bf16x2)
+// and the widening add issue at full rate, where one-at-a-time float<->half conversions queue on the
+// quarter-rate conversion unit, which bounded the 16-bit packers.
+template <typename T> __device__ __forceinline__ void round_pair(float &a, float &b);
+template <> __device__ __forceinline__ void round_pair<float>(float &, float &) {}
+template <> __device__ __forceinline__ void round_pair<__half>(float &a, float &b) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
+    a = f.x;
+    b = f.y;
+}
+template <> __device__ __forceinline__ void round_pair<__nv_bfloat16>(float &a, float &b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t u = *reinterpret_cast<const uint32_t *>(&h);
+    a = __uint_as_float(u << 16);
+    b = __uint_as_float(u & 0xFFFF0000u);
+}
+// round-half-to-even of t (|t| < 2^22) and clamp to [0, 15], as an integer: adding 1.5 * 2^23 leaves
+// the rounded integer in the low mantissa bits (the same result as rintf + clamp + convert; NaN -> 0)
+__device__ __forceinline__ int round_clamp_q(float t) {
+    t = fminf(fmaxf(t, -1.0f), 16.0f);                 // keeps the sum in range; NaN becomes -1 -> 0 below
+    const int q = __float_as_int(__fadd_rn(t, 12582912.0f)) - 0x4B400000;
+    return min(max(q, 0), 15);
+}
+
 // Quantise the 32 values of one block.  Returns the fp16 scale bits and fills q[32].
 template <typename T>
 __device__ __forceinline__ uint16_t quantize_block(const float (&v)[QK], int (&q)[QK]) {
@@ -37,12 +61,14 @@ __device__ __forceinline__ uint16_t quantize_block(const float (&v)[QK], int (&q
     float d = RoundTo<T>::r(__fdiv_rn(amax, 7.0f));   // quantization.py:341
     if (nan || !(d > 0.0f)) d = 1.0f;                 // quantization.py:342 (NaN amax fails d > 0)
 #pragma unroll
-    for (int i = 0; i < QK; ++i) {
-        float t = RoundTo<T>::r(__fdiv_rn(v[i], d));  // quantization.py:347, one rounding per op
-        t = RoundTo<T>::r(__fadd_rn(t, 8.0f));
-        t = rintf(t);                                  // ties to even, as torch.round
-        t = fminf(fmaxf(t, 0.0f), 15.0f);              // NaN -> 0 (the reference's result is undefined)
-        q[i] = (int)t;
+    for (int i = 0; i < QK; i += 2) {
+        float t0 = __fdiv_rn(v[i], d), t1 = __fdiv_rn(v[i + 1], d);   // quantization.py:347, one rounding per op
+        round_pair<T>(t0, t1);
+        t0 = __fadd_rn(t0, 8.0f);
+        t1 = __fadd_rn(t1, 8.0f);
+        round_pair<T>(t0, t1);
+        q[i] = round_clamp_q(t0);                      // ties to even, as torch.round; NaN -> 0 (the
+        q[i + 1] = round_clamp_q(t1);                  // reference's result is undefined there)
     }
     return __half_as_ushort(__float2half_rn(d));      // quantization.py:355
 }
@@ -184,6 +210,8 @@ quantize_kn_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
 constexpr int QNK_KB = 8;
 constexpr int QNK_THREADS = TILE_N * QNK_KB * 4;
 
+constexpr int QNK_ITER = 1;            // groups of QNK_KB blocks per CTA (more than one measured slower: registers halve the CTAs per SM)
+
 template <typename T>
 __global__ void __launch_bounds__(QNK_THREADS)
 quantize_nk_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__restrict__ blocks,
@@ -196,94 +224,110 @@ quantize_nk_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
     const int kbl = (tid >> 2) & (QNK_KB - 1);
     const int r = tid >> 5;                // row within the 16-column tile (one warp per row)
     const int64_t KB = K / QK;
-    const int64_t NT = tiles_n(N);
     const int64_t nt = blockIdx.x;
-    const int64_t kb0 = (int64_t)blockIdx.y * QNK_KB;
-    const int64_t kb = kb0 + kbl;
     const int64_t n = nt * TILE_N + r;
-    const bool ok = kb < KB && n < N;
+    const int64_t n0 = nt * TILE_N;
+    const int g = r & 7, hi8 = r >> 3;
 
-    float v[8];
-    if (ok) {
-        const T *p = w + n * K + kb * QK + c * 8;     // 16-byte aligned when the base is (fp16/bf16), 32 for fp32
-        if constexpr (sizeof(T) == 4) {
-            float4 a = __ldg(reinterpret_cast<const float4 *>(p));
-            float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    // all of the CTA's loads first: a thread's QNK_ITER 16-byte (32-byte for fp32) pieces are 512
+    // (1024) bytes apart in its row
+    float v[QNK_ITER][8];
+    bool oks[QNK_ITER];
+#pragma unroll
+    for (int it = 0; it < QNK_ITER; ++it) {
+        const int64_t kb = ((int64_t)blockIdx.y * QNK_ITER + it) * QNK_KB + kbl;
+        oks[it] = kb < KB && n < N;
+        if (oks[it]) {
+            const T *p = w + n * K + kb * QK + c * 8;     // 16-byte aligned when the base is (fp16/bf16), 32 for fp32
+            if constexpr (sizeof(T) == 4) {
+                float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+                float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+                v[it][0] = a.x; v[it][1] = a.y; v[it][2] = a.z; v[it][3] = a.w;
+                v[it][4] = b.x; v[it][5] = b.y; v[it][6] = b.z; v[it][7] = b.w;
+            } else {
+                uint4 a = __ldg(reinterpret_cast<const uint4 *>(p));
+                const T *e = reinterpret_cast<const T *>(&a);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[it][i] = RoundTo<T>::ld(e + i);
+            }
         } else {
-            uint4 a = __ldg(reinterpret_cast<const uint4 *>(p));
-            const T *e = reinterpret_cast<const T *>(&a);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = RoundTo<T>::ld(e + i);
+            for (int i = 0; i < 8; ++i) v[it][i] = 0.0f;
         }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
-    float amax = 0.0f;
-    bool nan = false;
+
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float a = fabsf(v[i]);
-        nan |= (a != a);
-        amax = fmaxf(amax, a);
-    }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    int nan_i = nan ? 1 : 0;
-    nan_i |= __shfl_xor_sync(0xffffffffu, nan_i, 1);
-    nan_i |= __shfl_xor_sync(0xffffffffu, nan_i, 2);
-    nan = nan_i != 0;
-    float d = RoundTo<T>::r(__fdiv_rn(amax, 7.0f));
-    if (nan || !(d > 0.0f)) d = 1.0f;
-    uint32_t iw = 0x88888888u;
-    uint16_t dbits = 0;
-    if (ok) {
-        dbits = __half_as_ushort(__float2half_rn(d));
-        iw = 0;
+    for (int it = 0; it < QNK_ITER; ++it) {
+        const int64_t kb0 = ((int64_t)blockIdx.y * QNK_ITER + it) * QNK_KB;
+        if (kb0 >= KB) break;                              // uniform over the CTA
+        const int64_t kb = kb0 + kbl;
+        const bool ok = oks[it];
+        float amax = 0.0f;
+        bool nan = false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            float t = RoundTo<T>::r(__fdiv_rn(v[i], d));
-            t = RoundTo<T>::r(__fadd_rn(t, 8.0f));
-            t = fminf(fmaxf(rintf(t), 0.0f), 15.0f);
-            iw |= (uint32_t)(int)t << (4 * i);          // byte j = q[2j] | q[2j+1] << 4
+            float a = fabsf(v[it][i]);
+            nan |= (a != a);
+            amax = fmaxf(amax, a);
         }
-    }
-    const int g = r & 7, hi8 = r >> 3;
-    uint8_t *tile = s_tile[kbl >> 1];
-    *reinterpret_cast<uint32_t *>(tile + slot_of(g, c) * 16 + ((kbl & 1) * 2 + hi8) * 4) =
-        interchange_to_prepacked_word(iw);
-    if (c == 0) *reinterpret_cast<uint16_t *>(tile + TILE_QS_BYTES + g * 8 + ((kbl & 1) * 2 + hi8) * 2) = dbits;
-    const int64_t n0 = nt * TILE_N;
-    if (blocks != nullptr) {
-        const int shift = (int)((reinterpret_cast<uintptr_t>(blocks) + (size_t)(kb * N + n0) * BLOCK_BYTES) & 15);
-        uint16_t *sb = reinterpret_cast<uint16_t *>(&s_blk[kbl][shift + r * BLOCK_BYTES]);
-        if (c == 0) sb[0] = dbits;
-        sb[1 + 2 * c] = (uint16_t)(iw & 0xFFFF);
-        sb[2 + 2 * c] = (uint16_t)(iw >> 16);
-    }
-    __syncthreads();
-    if (prepacked != nullptr) {
-        // the CTA's four tiles are consecutive k tiles of one column tile: contiguous in memory
-        const int64_t ku0 = kb0 / TILE_KB;
-        const int64_t KU = tiles_k(K);
-        for (int i = tid; i < (QNK_KB / TILE_KB) * (TILE_BYTES / 16); i += QNK_THREADS) {
-            const int t = i / (TILE_BYTES / 16), o = i % (TILE_BYTES / 16);
-            if (ku0 + t < KU)
-                reinterpret_cast<uint4 *>(prepacked + tile_offset(nt, ku0 + t, KU))[o] =
-                    reinterpret_cast<const uint4 *>(&s_tile[t][0])[o];
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        int nan_i = nan ? 1 : 0;
+        nan_i |= __shfl_xor_sync(0xffffffffu, nan_i, 1);
+        nan_i |= __shfl_xor_sync(0xffffffffu, nan_i, 2);
+        nan = nan_i != 0;
+        float d = RoundTo<T>::r(__fdiv_rn(amax, 7.0f));
+        if (nan || !(d > 0.0f)) d = 1.0f;
+        uint32_t iw = 0x88888888u;
+        uint16_t dbits = 0;
+        if (ok) {
+            dbits = __half_as_ushort(__float2half_rn(d));
+            iw = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                float t0 = __fdiv_rn(v[it][i], d), t1 = __fdiv_rn(v[it][i + 1], d);
+                round_pair<T>(t0, t1);
+                t0 = __fadd_rn(t0, 8.0f);
+                t1 = __fadd_rn(t1, 8.0f);
+                round_pair<T>(t0, t1);
+                iw |= (uint32_t)round_clamp_q(t0) << (4 * i);          // byte j = q[2j] | q[2j+1] << 4
+                iw |= (uint32_t)round_clamp_q(t1) << (4 * i + 4);
+            }
         }
-    }
-    if (blocks != nullptr) {
-        const int ncols = (int)min((int64_t)TILE_N, N - n0);
-        // one warp per block row copies its 16 x 18 bytes
-        const int warp = tid >> 5, lane = tid & 31;
-        if (warp < QNK_KB && kb0 + warp < KB) {
-            uint8_t *dst = blocks + (size_t)((kb0 + warp) * N + n0) * BLOCK_BYTES;
-            const int shift = (int)(reinterpret_cast<uintptr_t>(dst) & 15);
-            copy_out_congruent(dst, &s_blk[warp][shift], ncols * BLOCK_BYTES, lane, 32);
+        uint8_t *tile = s_tile[kbl >> 1];
+        *reinterpret_cast<uint32_t *>(tile + slot_of(g, c) * 16 + ((kbl & 1) * 2 + hi8) * 4) =
+            interchange_to_prepacked_word(iw);
+        if (c == 0) *reinterpret_cast<uint16_t *>(tile + TILE_QS_BYTES + g * 8 + ((kbl & 1) * 2 + hi8) * 2) = dbits;
+        if (blocks != nullptr) {
+            const int shift = (int)((reinterpret_cast<uintptr_t>(blocks) + (size_t)(kb * N + n0) * BLOCK_BYTES) & 15);
+            uint16_t *sb = reinterpret_cast<uint16_t *>(&s_blk[kbl][shift + r * BLOCK_BYTES]);
+            if (c == 0) sb[0] = dbits;
+            sb[1 + 2 * c] = (uint16_t)(iw & 0xFFFF);
+            sb[2 + 2 * c] = (uint16_t)(iw >> 16);
         }
+        __syncthreads();
+        if (prepacked != nullptr) {
+            // the group's four tiles are consecutive k tiles of one column tile: contiguous in memory
+            const int64_t ku0 = kb0 / TILE_KB;
+            const int64_t KU = tiles_k(K);
+            for (int i = tid; i < (QNK_KB / TILE_KB) * (TILE_BYTES / 16); i += QNK_THREADS) {
+                const int t = i / (TILE_BYTES / 16), o = i % (TILE_BYTES / 16);
+                if (ku0 + t < KU)
+                    reinterpret_cast<uint4 *>(prepacked + tile_offset(nt, ku0 + t, KU))[o] =
+                        reinterpret_cast<const uint4 *>(&s_tile[t][0])[o];
+            }
+        }
+        if (blocks != nullptr) {
+            const int ncols = (int)min((int64_t)TILE_N, N - n0);
+            // one warp per block row copies its 16 x 18 bytes
+            const int warp = tid >> 5, lane = tid & 31;
+            if (warp < QNK_KB && kb0 + warp < KB) {
+                uint8_t *dst = blocks + (size_t)((kb0 + warp) * N + n0) * BLOCK_BYTES;
+                const int shift = (int)(reinterpret_cast<uintptr_t>(dst) & 15);
+                copy_out_congruent(dst, &s_blk[warp][shift], ncols * BLOCK_BYTES, lane, 32);
+            }
+        }
+        __syncthreads();                                    // the staging buffers are reused by the next group
     }
 }
 
@@ -403,7 +447,7 @@ static int launch_quantize(const void *w, int64_t K, int64_t N, int layout, uint
             quantize_kn_kernel<T, false><<<grid, QT_THREADS, 0, st>>>((const T *)w, K, N, blocks, prepacked);
     } else {
         if (!aligned(w, 16)) return Q4B_ERR_ALIGN;
-        dim3 grid((unsigned)tiles_n(N), (unsigned)ceil_div(K / QK, QNK_KB));
+        dim3 grid((unsigned)tiles_n(N), (unsigned)ceil_div(K / QK, QNK_KB * QNK_ITER));
         quantize_nk_kernel<T><<<grid, QNK_THREADS, 0, st>>>((const T *)w, K, N, blocks, prepacked);
     }
     Q4B_LAUNCH_CHECK();

@@ -29,7 +29,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: false when another role aborted or when this wait ran out, in which case it records
 // `code` in *status (first writer wins) and raises the CTA-wide abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
     for (int it = 1;; ++it) {
@@ -38,7 +39,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             const long long now = clock64();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_CYCLES) {
+            else if (now - t0 > limit_cycles) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;

@@ -211,12 +211,19 @@ def _matmul_prepacked(X: torch.Tensor, pre: Q4Prepacked, out: Optional[torch.Ten
         raise RuntimeError("out must be [M, N], X's dtype, unit inner stride")
     lib = _cabi.load()
     fn = {"auto": lib.q4b_matmul_addend, "gemv": lib.q4b_gemv_addend, "gemm": lib.q4b_gemm_addend}[kernel]
-    if addend is not None and (addend.dtype != torch.float32 or tuple(addend.shape) != (M, pre.N)
-                               or addend.stride(1) != 1 or addend.device != x.device):
-        raise RuntimeError("addend must be a float32 [M, N] tensor on X's device with unit inner stride")
+    ld_add = 0
+    if addend is not None:
+        if addend.dtype != torch.float32 or addend.device != x.device:
+            raise RuntimeError("addend must be a float32 tensor on X's device")
+        if addend.dim() == 1 and addend.numel() == pre.N and addend.is_contiguous():
+            ld_add = 0                       # one row added to every row of the result (a bias)
+        elif tuple(addend.shape) == (M, pre.N) and addend.stride(1) == 1:
+            ld_add = addend.stride(0) if M > 1 else pre.N
+        else:
+            raise RuntimeError("addend must be [M, N] with unit inner stride, or a contiguous [N] row")
     with torch.cuda.device(x.device):
         rc = fn(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.data.data_ptr(), pre.K, pre.N,
-                addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
+                addend.data_ptr() if addend is not None else None, ld_add,
                 y.data_ptr(), y.stride(0), flags, _cabi.stream_ptr(x.device))
     _cabi.check(rc, "matmul_ggml_q4_0")
     return y.float() if in_dtype == torch.float32 else y
@@ -326,7 +333,8 @@ class Int4GPrepacked:
 
 def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int = 128) -> Int4GPrepacked:
     """One-time conversion of a group-wise INT4 weight (cached on ``W_packed``).  Needs
-    ``K % 32 == 0`` and ``group_size % 32 == 0``, and scales inside fp16's range."""
+    ``K % 32 == 0`` and ``group_size % 32 == 0``, and scales inside fp16's range (checked on the
+    device; a scale beyond it raises instead of turning into ``inf``)."""
     key = (_version_of(W_packed), scales.data_ptr(), _version_of(scales), zeros.data_ptr(), _version_of(zeros), group_size)
     cached = getattr(W_packed, "_q4b_int4g", None)
     if cached is not None and cached[0] == key:
@@ -341,6 +349,13 @@ def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
         rc = _cabi.load().q4b_int4g_prepack(p.data_ptr(), s.data_ptr(), z.data_ptr(), _cabi.DTYPE_CODE[s.dtype], K, N,
                                             group_size, tiles.data_ptr(), corr.data_ptr(), _cabi.stream_ptr(p.device))
     _cabi.check(rc, "prepack_int4")
+    import ctypes
+    bad = ctypes.c_int(0)
+    with torch.cuda.device(p.device):
+        _cabi.check(_cabi.load().q4b_int4g_prepack_status(_cabi.stream_ptr(p.device), ctypes.byref(bad)), "prepack_int4")
+    if bad.value:
+        raise RuntimeError("prepack_int4: a group scale is outside float16's range (or NaN); the fused INT4 kernels "
+                           "store block scales as float16")
     out = Int4GPrepacked(Q4Prepacked(tiles, K, N), corr, group_size)
     try:
         W_packed._q4b_int4g = (key, out)
@@ -364,12 +379,14 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
     if M == 0:
         return torch.empty((0, N), dtype=in_dtype, device=x.device)
     addend = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    b32 = None
+    if bias is not None:
+        b32 = bias.to(device=x.device, dtype=torch.float32).contiguous()
     with torch.cuda.device(x.device):
         rc = _cabi.load().q4b_int4g_addend(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.corr.data_ptr(),
-                                           K, N, pre.group_size, addend.data_ptr(), _cabi.stream_ptr(x.device))
+                                           b32.data_ptr() if b32 is not None else None, K, N, pre.group_size,
+                                           addend.data_ptr(), _cabi.stream_ptr(x.device))
     _cabi.check(rc, "matmul_int4")
-    if bias is not None:
-        addend += bias.float()
     y = _matmul_prepacked(x, pre.tiles, addend=addend, flags=_ACT_FLAGS[activation])
     return y.float() if in_dtype == torch.float32 else y
 
@@ -386,8 +403,38 @@ def matmul_int4(X: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor, z
     X2 = X.reshape(-1, X.shape[-1]) if batched else X
     if X2.dim() != 2:
         raise RuntimeError("X must be [M, K] or [B, M, K]")
-    Y = _matmul_int4_prepacked(X2, prepack_int4(W_packed, scales, zeros, group_size), activation=activation)
+    K = W_packed.shape[0] * 2
+    if K % QK4_0 or group_size % QK4_0:
+        Y = _matmul_int4_generic(X2, W_packed, scales, zeros, group_size, activation)
+    else:
+        Y = _matmul_int4_prepacked(X2, prepack_int4(W_packed, scales, zeros, group_size), activation=activation)
     return Y.view(X.shape[0], X.shape[1], -1) if batched else Y
+
+
+def _matmul_int4_generic(X2: torch.Tensor, W_packed, scales, zeros, group_size: int, activation: Optional[str]) -> torch.Tensor:
+    """Shapes the streaming tiles do not cover (K or group_size not a multiple of 32), which the
+    reference's Python loop accepts (quantization.py:207-239): a CUDA-core kernel straight from the
+    ``[K/2, N]`` format, fp32 accumulation.  The activation, if any, is applied afterwards."""
+    K, N = _check_int4g(W_packed, scales, zeros, group_size)
+    in_dtype = X2.dtype
+    x = (X2.half() if in_dtype == torch.float32 else X2).contiguous()
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"X must be float16, bfloat16 or float32 (got {in_dtype})")
+    assert x.shape[1] == K, f"X K dim ({x.shape[1]}) must match weight K ({K})"
+    M = x.shape[0]
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if M:
+        p, s, z = W_packed.contiguous(), scales.contiguous(), zeros.contiguous()
+        with torch.cuda.device(x.device):
+            rc = _cabi.load().q4b_int4g_matmul_generic(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), p.data_ptr(),
+                                                       s.data_ptr(), z.data_ptr(), _cabi.DTYPE_CODE[s.dtype], K, N, group_size,
+                                                       y.data_ptr(), y.stride(0), _cabi.stream_ptr(x.device))
+        _cabi.check(rc, "matmul_int4")
+    if activation == "silu":
+        y = torch.nn.functional.silu(y.float()).to(y.dtype)
+    elif activation == "gelu":
+        y = torch.nn.functional.gelu(y.float(), approximate="tanh").to(y.dtype)
+    return y.float() if in_dtype == torch.float32 else y
 
 
 def matmul_int4_silu(X, W_packed, scales, zeros, group_size: int = 128) -> torch.Tensor:
@@ -486,10 +533,10 @@ class Int4Linear(nn.Module):
     ``extra_repr`` (quantization.py:457-612): ``weight_packed [in/2, out]``, ``scales`` /
     ``zeros [groups, out]`` and ``bias`` are the serialised state, so checkpoints interchange.
 
-    ``dequant_on_load=True`` (the reference's default) keeps a dense fp16 copy and multiplies with
-    it, like the reference's "hybrid" mode; ``keep_quantized()`` or ``dequant_on_load=False`` runs
-    the fused kernels on the packed weight (the reference's ``int4_kernel`` mode), bias included
-    as an fp32 term before the output rounding."""
+    The fused kernels on the packed weight are the default here (the reference's ``int4_kernel``
+    mode, bias included as an fp32 term before the output rounding): ``dequant_on_load`` is accepted
+    for signature compatibility, but a dense fp16 copy (the reference's "hybrid" mode, four times the
+    memory and a library GEMM) is made only by an explicit :meth:`dequantize` call."""
 
     def __init__(self, in_features: int, out_features: int, group_size: int = 128, bias: bool = True,
                  device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None,
@@ -531,8 +578,6 @@ class Int4Linear(nn.Module):
         q.zeros.copy_(zeros)
         if module.bias is not None:
             q.bias.copy_(module.bias.data)
-        if dequant_on_load:
-            q.dequantize()
         return q
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -541,6 +586,11 @@ class Int4Linear(nn.Module):
             y = (x_half @ self._weight_dequant).to(x.dtype)
             return y + self.bias if self.bias is not None else y
         lead = x.shape[:-1]
+        if self.in_features % QK4_0 or self.group_size % QK4_0:
+            y = _matmul_int4_generic(x.reshape(-1, x.shape[-1]), self.weight_packed, self.scales, self.zeros, self.group_size, None)
+            if self.bias is not None:
+                y = y + self.bias
+            return y.reshape(*lead, self.out_features)
         pre = prepack_int4(self.weight_packed, self.scales, self.zeros, self.group_size)
         y = _matmul_int4_prepacked(x.reshape(-1, x.shape[-1]), pre, bias=self.bias)
         if self.bias is not None and self.bias.dtype != y.dtype:
@@ -588,7 +638,7 @@ class Q4Linear(nn.Module):
         x2 = x.reshape(-1, x.shape[-1])
         addend = None
         if self.bias is not None and x2.shape[0] > 0:
-            addend = self.bias.float().unsqueeze(0).expand(x2.shape[0], -1).contiguous()
+            addend = self.bias.float().contiguous()           # one row, broadcast by the kernels' epilogues
         y = _matmul_prepacked(x2, prepack_ggml_q4_0(self.weight_blocks), addend=addend)
         return y.reshape(*lead, self.out_features)
 

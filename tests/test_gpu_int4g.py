@@ -125,9 +125,11 @@ def test_int4_errors(mo, cuda_dev):
         mo.quantize_int4(torch.zeros(64, 8), 32)                       # CPU tensor: no fallback
     with pytest.raises(RuntimeError):
         mo.quantize_int4(w, 31)                                        # odd group
-    p, s, zz = mo.quantize_int4(w + 1.0, 16)
-    with pytest.raises(RuntimeError):
-        mo.matmul_int4(torch.zeros(1, 64, device=cuda_dev, dtype=torch.float16), p, s, zz, 16)   # group % 32 != 0
+    big = torch.full((64, 8), 3.0e6, device=cuda_dev)
+    big[::2] = -3.0e6
+    p, s, zz = mo.quantize_int4(big, 32)                                  # scale 4e5: beyond fp16
+    with pytest.raises(RuntimeError, match="float16"):
+        mo.matmul_int4(torch.zeros(1, 64, device=cuda_dev, dtype=torch.float16), p, s, zz, 32)
     with pytest.raises(RuntimeError):                                  # CPU tensors: no fallback
         mo.matmul_int8(torch.zeros(1, 64), torch.zeros(64, 8, dtype=torch.int8), torch.ones(1, 8), torch.zeros(1, 8), 64)
 
@@ -198,3 +200,35 @@ def test_activation_on_q4_0_kernels_all_paths(mo, cuda_dev):
             y = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel=kernel, flags=flag | extra)
             assert orc.rel_l2(y, ref) <= TOL, (M, kernel, extra, flag)
     assert Q.wait_status(cuda_dev) == 0
+
+
+@pytest.mark.parametrize("K,gs", [(64, 16), (96, 48), (130, 26), (256, 100)])
+def test_matmul_int4_group_sizes_outside_the_tile_format(mo, cuda_dev, K, gs):
+    """K or group_size not a multiple of 32: the reference's loop takes them (quantization.py:207-239);
+    here a CUDA-core kernel reads the [K/2, N] format directly."""
+    g = torch.Generator().manual_seed(K + gs)
+    N = 37
+    w = torch.randn(K, N, generator=g) * 0.05
+    packed, scales, zeros = mo.quantize_int4(w.to(cuda_dev), gs)
+    wd = orc.dequantize_int4_groupwise(packed.cpu(), scales.cpu(), zeros.cpu(), gs, torch.float32)
+    for M in (1, 9):
+        x = torch.randn(M, K, generator=g).half()
+        y = mo.matmul_int4(x.to(cuda_dev), packed, scales, zeros, gs)
+        assert y.dtype == x.dtype and tuple(y.shape) == (M, N)
+        assert orc.rel_l2(y, x.float() @ wd) <= TOL
+    lin = torch.nn.Linear(K, N).to(cuda_dev)
+    ql = mo.Int4Linear.from_float(lin, group_size=gs)
+    xl = torch.randn(3, K, generator=g).to(cuda_dev)
+    assert orc.rel_l2(ql(xl), lin(xl)) <= 0.2                                  # the 4-bit quantisation error itself
+
+
+def test_int4_linear_default_runs_the_fused_kernels(mo, cuda_dev):
+    lin = torch.nn.Linear(256, 48).to(cuda_dev)
+    ql = mo.Int4Linear.from_float(lin)                                         # reference defaults
+    assert ql._weight_dequant is None and "int4_kernel" in ql.extra_repr()
+    x = torch.randn(70000, 256, device=cuda_dev).half()                        # more rows than a grid dimension holds
+    y = ql(x)
+    assert tuple(y.shape) == (70000, 48)
+    assert orc.rel_l2(y[:64], lin(x[:64].float())) <= 0.2
+    ql.dequantize()
+    assert "fast_fp16" in ql.extra_repr()

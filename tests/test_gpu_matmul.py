@@ -87,18 +87,25 @@ def test_config2_llama7b_decode(mo, cuda_dev, K, N, M):
     check(mo, cuda_dev, w, x, TOL_F16)
 
 
+@pytest.mark.parametrize("M", [1, 128])
 @pytest.mark.parametrize("K,N", [(8192, 28672), (28672, 8192)])
-def test_config4_llama70b_decode_column_sample(mo, cuda_dev, K, N):
-    """Full-size 70B-shaped layer at M = 1; the oracle is evaluated on a seeded sample of
-    1024 columns (the CPU product over all columns would take minutes)."""
+def test_config4_llama70b_column_sample(mo, cuda_dev, K, N, M):
+    """Full-size 70B-shaped layer at M = 1 and 128; the oracle is evaluated on a seeded sample of
+    columns (and rows), since the CPU product over everything would take minutes."""
     g = torch.Generator().manual_seed(1004)
     w = (torch.randn(K, N, generator=g) * 0.015).half()
-    x = torch.randn(1, K, generator=g).half()
+    x = torch.randn(M, K, generator=g).half()
     blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
     y = mo.matmul_ggml_q4_0(x.to(cuda_dev), blocks)
-    cols = torch.randperm(N, generator=g)[:1024].sort().values
-    ref = c_oracle.matmul_f32(x, blocks[:, cols.to(cuda_dev)].cpu().contiguous())
-    assert orc.rel_l2(y[:, cols.to(cuda_dev)], ref) <= TOL_F16
+    cols = torch.randperm(N, generator=g)[:1024 if M == 1 else 256].sort().values
+    rows = torch.arange(M) if M == 1 else torch.randperm(M, generator=g)[:16].sort().values
+    ref = c_oracle.matmul_f32(x[rows].contiguous(), blocks[:, cols.to(cuda_dev)].cpu().contiguous())
+    assert orc.rel_l2(y[rows.to(cuda_dev)][:, cols.to(cuda_dev)], ref) <= TOL_F16
+    if M > 1:
+        # checksum over the full output: column sums commute with the product
+        wd = mo.dequantize_ggml_q4_0(blocks, torch.float32)
+        assert orc.rel_l2(y.float().sum(0, keepdim=True), x.to(cuda_dev).float().sum(0, keepdim=True) @ wd) <= TOL
+        return
     # linearity, a size-independent property of the full output: Y(2x) = 2 Y(x) up to output rounding
     y2 = mo.matmul_ggml_q4_0((2 * x).to(cuda_dev), blocks)
     assert orc.rel_l2(y2, 2 * y) <= 5e-4
@@ -216,7 +223,7 @@ def test_config3_prefill_with_outliers(mo, cuda_dev, M):
     print(f"config3 M={M} rel-L2 {err:.2e}")
 
 
-@pytest.mark.parametrize("M", [32, 128, 4096])
+@pytest.mark.parametrize("M", [1, 2, 8, 32, 128, 512, 4096])
 def test_config5_gemm_sweep(mo, cuda_dev, M):
     from metalops_b200 import quantization as Q
     w, x = make_case(1005 + M, M, 4096, 14336, torch.float16)
@@ -224,7 +231,7 @@ def test_config5_gemm_sweep(mo, cuda_dev, M):
     y = mo.matmul_ggml_q4_0(x.to(cuda_dev), blocks)
     assert Q.wait_status(cuda_dev) == 0
     g = torch.Generator().manual_seed(M)
-    rows = torch.randperm(M, generator=g)[:32].sort().values
+    rows = torch.randperm(M, generator=g)[:min(M, 32)].sort().values
     cols = torch.randperm(14336, generator=g)[:2048].sort().values
     ref = c_oracle.matmul_f32(x[rows].contiguous(), blocks[:, cols.to(cuda_dev)].cpu().contiguous())
     assert orc.rel_l2(y[rows.to(cuda_dev)][:, cols.to(cuda_dev)], ref) <= TOL_F16
@@ -251,3 +258,46 @@ def test_small_batch_tensor_memory_kernel(mo, cuda_dev, M, K, N, xdtype):
     assert torch.equal(y, y2), "two runs differ bitwise"
     y16 = Q._matmul_prepacked(x[:16].to(cuda_dev), pre, kernel="gemv")
     assert orc.rel_l2(y[:16], y16.float().cpu()) <= TOL
+
+
+def test_quantize_and_matmul_under_inference_mode(mo, cuda_dev):
+    """Inference tensors keep no version counter; the cache of the streaming-layout copy must not
+    depend on one."""
+    w, x = make_case(77, 3, 256, 80, torch.float16)
+    with torch.inference_mode():
+        blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+        y = mo.matmul_ggml_q4_0(x.to(cuda_dev), blocks)
+        lin = mo.Q4Linear.from_float(torch.nn.Linear(256, 80).to(cuda_dev))
+        lin(x.to(cuda_dev).float())
+    assert orc.rel_l2(y, c_oracle.matmul_f32(x, blocks.cpu())) <= TOL_F16
+    # a blocks tensor that arrives without a cached copy (e.g. from a checkpoint), created in inference mode
+    with torch.inference_mode():
+        fresh = blocks.clone()
+        assert torch.equal(mo.matmul_ggml_q4_0(x.to(cuda_dev), fresh), y)
+
+
+def test_both_activation_flags_are_rejected(mo, cuda_dev):
+    from metalops_b200 import _cabi
+    lib = _cabi.load()
+    w, x = make_case(5, 1, 64, 32, torch.float16)
+    pre = mo.prepack_ggml_q4_0(mo.quantize_ggml_q4_0(w.to(cuda_dev)))
+    xd, y = x.to(cuda_dev), torch.empty(1, 32, dtype=torch.float16, device=cuda_dev)
+    both = _cabi.FLAG_ACT_SILU | _cabi.FLAG_ACT_GELU
+    for fn in (lib.q4b_gemv, lib.q4b_gemm, lib.q4b_matmul):
+        assert fn(xd.data_ptr(), _cabi.F16, 1, 64, pre.data.data_ptr(), 64, 32, y.data_ptr(), 32, both, None) == _cabi.ERR_ARG
+
+
+def test_bias_row_vector_addend_all_kernels(mo, cuda_dev):
+    """A bias enters the epilogues as one fp32 row (leading dimension 0), not as an [M, N] tensor."""
+    from metalops_b200 import quantization as Q
+    g = torch.Generator().manual_seed(12)
+    K, N = 512, 272
+    w = torch.randn(K, N, generator=g) * 0.05
+    bias = torch.randn(N, generator=g)
+    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+    pre = mo.prepack_ggml_q4_0(blocks)
+    for M in (1, 5, 12, 40, 200):
+        x = torch.randn(M, K, generator=g).half()
+        y = Q._matmul_prepacked(x.to(cuda_dev), pre, addend=bias.to(cuda_dev))
+        ref = c_oracle.matmul_f32(x, blocks.cpu()) + bias
+        assert orc.rel_l2(y, ref) <= TOL_F16, M

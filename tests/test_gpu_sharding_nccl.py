@@ -1,4 +1,4 @@
-"""Column-parallel q4_0 layer on real GPUs over NCCL (needs >= 2 GPUs; skipped otherwise).
+"""Column-parallel q4_0 layer on real GPUs over NCCL (2, 4 and 8 ranks; skipped where the box has fewer GPUs).
 Each rank quantizes only its column shard (blocks are per column, so sharding over N changes no
 packed bit); the gathered result must equal each rank's local slice bit for bit and the single-GPU
 product within rounding (the launch plan, hence the order of the k-split sums, may depend on N).
@@ -62,14 +62,14 @@ def _worker(rank: int, world: int, port: int, ret):
         dist.destroy_process_group()
 
 
-def test_column_parallel_nccl_world2():
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_column_and_row_parallel_nccl(world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, 29650 + os.getpid() % 200, ret), nprocs=world, join=True)
-    assert dict(ret) == {0: True, 1: True}
+    assert dict(ret) == {r: True for r in range(world)}
 
 
 @pytest.mark.parametrize("M,dtype", [(1, torch.float16), (1, torch.bfloat16), (6, torch.float16), (13, torch.bfloat16)])
