@@ -30,7 +30,7 @@ namespace q4b {
 namespace gemm {
 
 constexpr int BM = 256, BN = 256, BK = 64, HALF_M = 128;
-constexpr int SA = 3, SB = 2;                        // ring depths of the X and B operand stages
+constexpr int SA = 3, SB = 3;                        // ring depths of the X and B operand stages
 constexpr int SW_MAX = 16;                           // packed-weight ring: depth chosen per launch, see w_ring_depth
 constexpr int A_BYTES = BM * BK * 2;                 // 32768
 constexpr int A_HALF_BYTES = HALF_M * BK * 2;        // 16384
@@ -192,7 +192,7 @@ struct RingPos {
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked,
-                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int bn,
+                    uint16_t *__restrict__ y, int M, int N, int K, int64_t ldy, int vec_store, int num_nt, int bn_max,
                     const float *__restrict__ addend, int64_t ld_add, int act) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
@@ -232,11 +232,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
     const uint32_t tmem_base = s_tmem_base;
 
     const int NT = (int)tiles_n(N);                    // prepacked 16-column tiles
-    // bn = columns per tile (multiple of 32, at most BN), chosen by the host to even out the waves
-    const int w_tiles = bn / TILE_N;
-    const int sw = w_ring_depth(bn);                   // packed-weight ring: depth and stage size
-    const int w_stage = w_tiles * TILE_BYTES;
-    const int num_mt = (M + BM - 1) / BM, num_nt = (N + bn - 1) / bn;
+    // The NT sixteen-column units are dealt to num_nt tiles as evenly as possible (widths differ by at
+    // most one unit, none wider than bn_max): the host picks num_nt so that the tile count fills whole
+    // waves of CTAs, which a single fixed width rarely does.
+    auto unit0 = [&](int i) { return (int)((long long)i * NT / num_nt); };
+    const int sw = w_ring_depth(bn_max);               // packed-weight ring: depth and stage size
+    const int w_stage = (bn_max / TILE_N) * TILE_BYTES;
+    const int num_mt = (M + BM - 1) / BM;
     const int num_tiles = num_mt * num_nt;
     const int k_steps = (K + BK - 1) / BK;
 
@@ -260,8 +262,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         // one thread working through them (which was slower than the MMAs they feed).
         RingPos w;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            const int nt0 = (t / num_mt) * w_tiles;
-            const int valid = min(w_tiles, NT - nt0);
+            const int nt0 = unit0(t / num_mt);
+            const int valid = unit0(t / num_mt + 1) - nt0;
             // the step's column tiles are k_steps tiles apart in the column-tile-major layout
             const uint8_t *src = prepacked + tile_offset(nt0 + min(lane, valid - 1), 0, k_steps);
             for (int ks = 0; ks < k_steps; ++ks) {
@@ -279,11 +281,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         // The whole warp runs the loop, converged, and one elected lane issues: the operands of
         // tcgen05.mma then live in uniform registers instead of being moved there per instruction.
         {
-            const uint32_t idesc = make_idesc(BF16, HALF_M, bn);
             RingPos a, b;
             uint32_t tphase = 0;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 const int mt = t % num_mt;
+                const uint32_t idesc = make_idesc(BF16, HALF_M, (unit0(t / num_mt + 1) - unit0(t / num_mt)) * TILE_N);
                 const int halves = (M - mt * BM > HALF_M) ? 2 : 1;     // skip an all-padding lower half
                 if (!mbar_wait_warp(bar_tempty, tphase ^ 1, abort_flag, 2, lane)) goto done;
                 tc_fence_after();
@@ -320,12 +322,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
             const int halves = (M - mt * BM > HALF_M) ? 2 : 1;
             if (!mbar_wait_warp<256>(bar_tfull, tphase, abort_flag, 5, lane)) goto done;
             tc_fence_after();
-            const int n_base = nt * bn;
+            const int n_base = unit0(nt) * TILE_N;
+            const int n_end = min(N, unit0(nt + 1) * TILE_N);          // this tile's columns end here
+            const int bn = unit0(nt + 1) * TILE_N - n_base;
             for (int h = 0; h < halves; ++h) {
                 const int m = mt * BM + h * HALF_M + quad * 32 + lane;
                 uint16_t *yrow = y + (size_t)m * ldy;
 #pragma unroll 1
-                for (int ch = grp; ch < bn / 32; ch += 2) {
+                for (int ch = grp; ch < (bn + 31) / 32; ch += 2) {
                     uint32_t r[32];
                     tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN + ch * 32), r);
                     tc_wait_ld();
@@ -334,27 +338,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
                         const float *arow = addend + (size_t)m * ld_add + n0;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (n0 + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + arow[j]);
+                            if (n0 + j < n_end) r[j] = __float_as_uint(__uint_as_float(r[j]) + arow[j]);
                     }
                     if (act != 0) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(apply_act(__uint_as_float(r[j]), act));
                     }
-                    if (m < M && n0 < N) {
-                        if (vec_store && n0 + 32 <= N) {
+                    if (m < M && n0 < n_end) {
+                        const int cols = min(32, n_end - n0);              // a tile's last chunk may be half full
+                        if (vec_store && cols % 8 == 0) {
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
-                                uint4 o;
-                                o.x = pack2_out<BF16>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                                o.y = pack2_out<BF16>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                                o.z = pack2_out<BF16>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                                o.w = pack2_out<BF16>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                                *reinterpret_cast<uint4 *>(yrow + n0 + 8 * v) = o;
+                                if (8 * v < cols) {
+                                    uint4 o;
+                                    o.x = pack2_out<BF16>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                                    o.y = pack2_out<BF16>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                    o.z = pack2_out<BF16>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                    o.w = pack2_out<BF16>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                    *reinterpret_cast<uint4 *>(yrow + n0 + 8 * v) = o;
+                                }
                             }
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (n0 + j < N) yrow[n0 + j] = (uint16_t)(pack2_out<BF16>(__uint_as_float(r[j]), 0.0f) & 0xFFFF);
+                                if (j < cols) yrow[n0 + j] = (uint16_t)(pack2_out<BF16>(__uint_as_float(r[j]), 0.0f) & 0xFFFF);
                         }
                     }
                 }
@@ -380,7 +387,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *_
         constexpr int TILES_PER_WARP = W_TILES / NUM_DEQ_WARPS;      // tile dw + i*NUM_DEQ_WARPS, i < TILES_PER_WARP
         RingPos w, b;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            const int valid = min(w_tiles, NT - (t / num_mt) * w_tiles);
+            const int valid = unit0(t / num_mt + 1) - unit0(t / num_mt);
             for (int ks = 0; ks < k_steps; ++ks) {
                 if (!mbar_wait_warp(bar_full_w(w.s), w.phase, abort_flag, 6, lane)) goto done;
                 if (!mbar_wait_warp(bar_empty_b(b.s), b.phase ^ 1, abort_flag, 8, lane)) goto done;
@@ -461,15 +468,20 @@ static EncodeTiledFn get_encode_fn() {
 template <bool BF16>
 static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M, int N, int K, int64_t ldy,
                   int vec_store, int sms, const float *addend, int64_t ld_add, int act, cudaStream_t st) {
-    // Columns per tile: the candidate that needs the least (waves x tile width), with a small
-    // bias towards wide tiles, whose MMAs and X loads are the more efficient.
+    // Tiles per row block: the count that needs the least (waves x (widest tile + fixed cost)).  A 64-k
+    // step costs its MMAs, proportional to the tile's width, plus about what 160 columns of MMAs cost
+    // (measured: operand traffic from L2 and the hand-overs between the roles do not shrink with the
+    // tile), so wide tiles win unless a narrower width fills the last wave.
     const int mt = (M + BM - 1) / BM;
-    int bn = BN;
+    const int units = (int)tiles_n(N);
+    int num_nt = (units + BN / TILE_N - 1) / (BN / TILE_N), bn_max = BN;
     long best = -1;
-    for (int cand = BN; cand >= 32; cand -= 32) {
-        const long t = (long)mt * ((N + cand - 1) / cand);
-        const long cost = ((t + sms - 1) / sms) * (cand + 24);
-        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    for (int cand = num_nt; cand <= units; ++cand) {
+        const int widest = ((units + cand - 1) / cand) * TILE_N;
+        const long waves = ((long)mt * cand + sms - 1) / sms;
+        const long cost = waves * (widest + 160);
+        if (best < 0 || cost < best) { best = cost; num_nt = cand; bn_max = widest; }
+        if (widest <= 2 * TILE_N) break;
     }
     {   // opt in to the large dynamic shared memory once per device and instantiation
         static bool attr_done[64] = {};
@@ -482,10 +494,10 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, void *y, int M
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    const int tiles = mt * ((N + bn - 1) / bn);
+    const int tiles = mt * num_nt;
     const int grid = tiles < sms ? tiles : sms;
     gemm_tcgen05_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, (uint16_t *)y, M, N, K,
-                                                             ldy, vec_store, bn, addend, ld_add, act);
+                                                             ldy, vec_store, num_nt, bn_max, addend, ld_add, act);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }
