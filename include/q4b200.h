@@ -119,11 +119,13 @@ Q4B_API int q4b_dequantize(const void *blocks, int64_t K, int64_t N, void *w_out
  *   q4b_gemv   decode path, 1 <= M <= 16: streams the prepacked tiles once (bulk asynchronous
  *              copies into per-warp rings, 128-bit reads), dequantises in registers,
  *              warp-level mma + split-K reduction in the CTA.
- *   q4b_gemm   prefill path, any M >= 1 (intended for M >= 17): TMA -> shared memory ->
- *              dequantise to bf16/fp16 -> tcgen05.mma with TMEM accumulators.
+ *   q4b_gemm   prefill path, any M >= 1 (intended for M >= 17): the packed weights are
+ *              dequantised to bf16/fp16 straight into tensor memory and are the A operand of
+ *              tcgen05.mma, X tiles arrive by TMA, accumulators in tensor memory.  Up to 128
+ *              rows a CTA per 128-column panel and k range; above, persistent CTAs over items
+ *              of 128 columns x up to 256 rows.
  *   q4b_matmul picks q4b_gemv for M <= 8, and for 9 <= M <= 16 when the weight has fewer than
- *              2^25 elements; otherwise q4b_gemm (which itself runs a tensor-memory kernel with the
- *              weights as the tcgen05 A operand for M <= 128).
+ *              2^25 elements; otherwise q4b_gemm.
  * A flags word with both activation bits set is rejected with Q4B_ERR_ARG.
  */
 Q4B_API int q4b_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
@@ -148,6 +150,11 @@ Q4B_API int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, 
 Q4B_API int q4b_matmul_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
                               const void *prepacked, int64_t K, int64_t N, const float *addend,
                               int64_t ld_add, void *y, int64_t ldy, int flags, void *stream);
+/* The same product forced onto the persistent prefill kernel (items of 128 columns x up to 256 rows x
+ * all of k; any M >= 1), which q4b_gemm_addend uses above 128 rows. */
+Q4B_API int q4b_gemm_wt_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+                               int64_t K, int64_t N, const float *addend, int64_t ld_add, void *y,
+                               int64_t ldy, int flags, void *stream);
 
 /*
  * Group-wise asymmetric INT4 format of the reference (quantization.py:26-239; its Metal
@@ -299,8 +306,9 @@ Q4B_API int q4b_rmsnorm(const void *x, int dtype, int64_t M, int64_t K, int64_t 
  * The matmul kernels bound every mbarrier wait; a wait that gives up makes the kernel set a
  * status word on the device and stop early (its output is then incomplete).  This call
  * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with
- * *detail (may be NULL) = which wait gave up (1..8 prefill kernel roles, 100-101 decode kernels,
- * 401-407 small-batch tensor-memory kernel, 500-504 persistent single-row kernel, 900 self-test).
+ * *detail (may be NULL) = which wait gave up (100-101 decode kernels, 401-407 small-batch
+ * tensor-memory kernel, 500-504 persistent single-row kernel, 601-608 persistent prefill kernel,
+ * 900 self-test).
  * It never traps or faults the device.
  */
 Q4B_API int q4b_wait_status(void *stream, int *detail);

@@ -66,6 +66,7 @@ SYMBOLS = {
     "q4b_matmul_host_noalloc": (_ci, [_vp, _ci, _i64, _vp, _i64, _i64, _vp, _vp]),
     "q4b_gemv_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _ci, _vp]),
     "q4b_gemm_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _ci, _vp]),
+    "q4b_gemm_wt_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _ci, _vp]),
     "q4b_matmul_addend": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _ci, _vp]),
     "q4b_int4g_quantize": (_ci, [_vp, _ci, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "q4b_int4g_dequantize": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _ci, _vp]),

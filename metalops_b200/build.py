@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq4b200.so")
-SOURCES = ["q4b_capi.cu", "q4b_int8g.cu", "q4b_quantize.cu", "q4b_gemv.cu", "q4b_chain.cu", "q4b_gemm_sm100.cu", "q4b_gemm_tmem.cu", "q4b_int4g.cu", "q4b_rmsnorm.cu"]
+SOURCES = ["q4b_capi.cu", "q4b_int8g.cu", "q4b_quantize.cu", "q4b_gemv.cu", "q4b_chain.cu", "q4b_gemm.cu", "q4b_gemm_tmem.cu", "q4b_gemm_wt.cu", "q4b_int4g.cu", "q4b_rmsnorm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

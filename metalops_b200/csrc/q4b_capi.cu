@@ -1,5 +1,5 @@
 // C-ABI glue: status strings, device checks, the M-based dispatcher and the host-buffer
-// convenience entry.  The kernels live in q4b_quantize.cu, q4b_gemv.cu and q4b_gemm_sm100.cu.
+// convenience entry.  The kernels live in q4b_quantize.cu, q4b_gemv.cu, q4b_gemm_tmem.cu and q4b_gemm_wt.cu.
 #include <cstdio>
 #include <cstring>
 #include <mutex>

@@ -1,0 +1,83 @@
+// Entry points of the tensor-core matmul (more rows than the decode kernels take) and the status of the
+// library's bounded waits.
+//
+// Replaces the reference's dispatch to its simdgroup kernel matmul_ggml_q4_0
+// (packages/metalcore/src/metalcore/native/core_mps.mm:5917-5975, kernel quant_kernels.metal:1738-1886).
+// Both kernels behind q4b_gemm keep the dequantised weights in tensor memory as the tcgen05 A operand:
+//   M <= 128   q4b_gemm_tmem.cu: a CTA per 128-column panel and k range (clusters split k), whose cost per
+//              k-tile does not depend on M, unless the weight has more panels than two per SM;
+//   otherwise  q4b_gemm_wt.cu: persistent CTAs over items of 128 columns x up to 256 rows x all of k.
+#include "q4b_common.cuh"
+
+namespace q4b {
+
+int device_sm_count();
+int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                     const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
+int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, const float *addend,
+                   int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
+int gemv_wait_status(int *value);
+int gemm_tmem_wait_status(int *value);
+int gemm_wt_wait_status(int *value);
+namespace chain { int wait_status(int *value); }
+int selftest_wait_status(int *value);
+
+// argument checks shared by q4b_gemm_addend and q4b_gemm_wt_addend
+static int check_gemm_args(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                           const float *addend, int64_t ld_add, const void *y, int64_t ldy, int flags) {
+    // ld_add == 0: the addend is one row of N values added to every row of the result (a bias)
+    if (addend != nullptr && ld_add != 0 && ld_add < N) return Q4B_ERR_ARG;
+    if (x == nullptr || prepacked == nullptr || y == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || K <= 0 || N <= 0 || ldx < K || ldy < N) return Q4B_ERR_ARG;
+    if (act_of_flags(flags) == 3) return Q4B_ERR_ARG;
+    if (K % QK || M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return Q4B_ERR_SHAPE;
+    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    if (!aligned(x, 16) || (ldx % 8) || !aligned(prepacked, 16) || !aligned(y, 2)) return Q4B_ERR_ALIGN;
+    if (q4b_device_ok() != Q4B_OK) return Q4B_ERR_ARCH;
+    return Q4B_OK;
+}
+
+}  // namespace q4b
+
+using namespace q4b;
+
+extern "C" int q4b_gemm(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                        int64_t N, void *y, int64_t ldy, int flags, void *stream) {
+    return q4b_gemm_addend(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, y, ldy, flags, stream);
+}
+
+extern "C" int q4b_gemm_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                               int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
+                               void *stream) {
+    if (int rc = check_gemm_args(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags)) return rc;
+    if (M <= 128 && ceil_div(tiles_n(N), 8) <= 2 * device_sm_count())
+        return gemm_tmem_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags,
+                                (cudaStream_t)stream);
+    return gemm_wt_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, (cudaStream_t)stream);
+}
+
+// The persistent kernel whatever M: same arguments and checks as q4b_gemm_addend.
+extern "C" int q4b_gemm_wt_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                                  int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
+                                  void *stream) {
+    if (int rc = check_gemm_args(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags)) return rc;
+    return gemm_wt_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, (cudaStream_t)stream);
+}
+
+// Synchronises the stream, then reads and clears the status words of every kernel with bounded waits.
+extern "C" int q4b_wait_status(void *stream, int *detail) {
+    Q4B_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    int h = 0, hv = 0;
+    if (int rc = gemv_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = gemm_tmem_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = gemm_wt_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = chain::wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (int rc = selftest_wait_status(&hv)) return rc;
+    if (h == 0) h = hv;
+    if (detail) *detail = h;
+    return h != 0 ? Q4B_ERR_TIMEOUT : Q4B_OK;
+}

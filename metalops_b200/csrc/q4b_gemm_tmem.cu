@@ -1,7 +1,7 @@
 // Small-batch path: Y[M, N] = X[M, K] . dequant(W) for M <= 128 with the WEIGHTS as the tensor
 // cores' A operand in tensor memory ("swap A and B").
 //
-// Same contraction as q4b_gemm_sm100.cu (reference kernel:
+// Same contraction as q4b_gemm_wt.cu (reference kernel:
 // packages/metalcore/src/metalcore/native/quant_kernels.metal:1738-1886).  With few rows the
 // prefill kernel's 128-row X tile is mostly padding and every 64-k step pays a fixed ~850 cycles;
 // here the 128 lanes of tensor memory are 128 OUTPUT COLUMNS instead, so the work per step does not

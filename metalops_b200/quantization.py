@@ -210,7 +210,8 @@ def _matmul_prepacked(X: torch.Tensor, pre: Q4Prepacked, out: Optional[torch.Ten
     if y.shape != (M, pre.N) or y.dtype != x.dtype or y.stride(1) != 1:
         raise RuntimeError("out must be [M, N], X's dtype, unit inner stride")
     lib = _cabi.load()
-    fn = {"auto": lib.q4b_matmul_addend, "gemv": lib.q4b_gemv_addend, "gemm": lib.q4b_gemm_addend}[kernel]
+    fn = {"auto": lib.q4b_matmul_addend, "gemv": lib.q4b_gemv_addend, "gemm": lib.q4b_gemm_addend,
+          "gemm_wt": lib.q4b_gemm_wt_addend}[kernel]
     ld_add = 0
     if addend is not None:
         if addend.dtype != torch.float32 or addend.device != x.device:

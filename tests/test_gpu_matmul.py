@@ -190,6 +190,37 @@ def test_gemm_single_row_through_prefill_kernel(mo, cuda_dev):
     check_gemm(mo, cuda_dev, w, x, TOL_F16)
 
 
+@pytest.mark.parametrize("xdtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N", [
+    (1, 64, 16), (17, 32, 8), (129, 96, 48),          # one k-tile, half a k-tile, an odd number of k-tiles
+    (256, 448, 520), (257, 192, 130), (300, 1056, 1000),   # row-tile boundaries: 256, 2 x 144, 2 x 160 rows
+    (513, 2080, 272), (1000, 320, 4112), (2048, 4096, 384),
+])
+def test_persistent_prefill_kernel_forced(mo, cuda_dev, M, K, N, xdtype):
+    """The persistent kernel (items of 128 columns x up to 256 rows) at any M: stages of one and two
+    k-tiles, partial panels, partial row tiles; bitwise equal to what the dispatching entry gives."""
+    from metalops_b200 import quantization as Q
+    w, x = make_case(M + K + N, M, K, N, xdtype)
+    tol = TOL_F16 if xdtype == torch.float16 else TOL
+    check(mo, cuda_dev, w, x, tol, kernel="gemm_wt")
+    assert Q.wait_status(cuda_dev) == 0
+    blocks = mo.quantize_ggml_q4_0(w.to(cuda_dev))
+    pre = mo.prepack_ggml_q4_0(blocks)
+    g = torch.Generator().manual_seed(M)
+    add = torch.randn(M, N, generator=g).to(cuda_dev)
+    ya = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm_wt", addend=add, flags=_cabi_flags().FLAG_ACT_SILU)
+    v = c_oracle.matmul_f32(x, blocks.cpu()) + add.cpu()
+    assert orc.rel_l2(ya, v / (1.0 + torch.exp(-v))) <= 2 * tol
+    yb = Q._matmul_prepacked(x.to(cuda_dev), pre, kernel="gemm_wt", addend=add[0].contiguous())
+    assert orc.rel_l2(yb, c_oracle.matmul_f32(x, blocks.cpu()) + add[0].cpu()) <= tol
+    assert Q.wait_status(cuda_dev) == 0
+
+
+def _cabi_flags():
+    from metalops_b200 import _cabi
+    return _cabi
+
+
 def test_golden_matmul_prefill(mo, cuda_dev):
     z = load_golden("q4_0_matmul.npz")
     x = golden_tensor(z, "b_m70.x")
