@@ -59,7 +59,7 @@ def recorded_traffic():
     recorded from profiler captures of small cases; the bench itself never runs under a profiler.
     decode: DRAM bytes per algorithmic byte of the persistent single-row kernel;
     gemm: bytes of one M=2048, K=4096, N=14336 launch."""
-    return {"decode_dram_bytes_per_algorithmic_byte": 1.00, "gemm_dram_bytes_per_launch": 62.1e6}
+    return {"decode_dram_bytes_per_algorithmic_byte": 1.00, "gemm_dram_bytes_per_launch": 87.9e6}
 
 
 def cpu_model() -> str:
@@ -609,7 +609,7 @@ def bench_gemm(dev, stream, lib, peaks, traffic, local):
             "dtype": "bf16",
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0, "peak_source": peaks["source"],
-                         "kernel": "gemm_tcgen05_kernel", "traffic": traffic.get("gemm_dram_bytes_per_launch"),
+                         "kernel": "gemm_wt_kernel", "traffic": traffic.get("gemm_dram_bytes_per_launch"),
                          "note": f"{reps}-launch burst against the burst cuBLAS figure"},
             "clocks": clk.summary(),
             "sustained": {"value": tf_long, "unit": "TFLOP/s", "launches": n_long, "seconds": ms_long * n_long / 1e3,
@@ -812,7 +812,7 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
 
 
 def run_probe(spec: str) -> None:
-    """`--probe MxKxN`: six distinct weights, one q4b_matmul launch each (fp16 activations), then the
+    """`--probe MxKxN`: six distinct weights, a warm-up launch and then one q4b_matmul launch each (fp16 activations), then the
     wait status; prints the average device time.  `--probe chain:L`: L layers of the 7B-shaped stage
     list, three runs.  Small fixed cases for profiler captures."""
     from metalops_b200 import _cabi
@@ -842,7 +842,8 @@ def run_probe(spec: str) -> None:
     y = torch.empty(M, N, device=dev, dtype=torch.float16)
     sp = _cabi.stream_ptr(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize(dev)
+    _cabi.check(lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, pres[0].data.data_ptr(), K, N, y.data_ptr(), N, 0, sp), "q4b_matmul")
+    torch.cuda.synchronize(dev)                  # the first launch pays the one-time set-up
     e0.record()
     for p in pres:
         _cabi.check(lib.q4b_matmul(x.data_ptr(), _cabi.F16, M, K, p.data.data_ptr(), K, N, y.data_ptr(), N, 0, sp), "q4b_matmul")
