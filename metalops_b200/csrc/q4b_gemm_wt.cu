@@ -52,7 +52,7 @@ constexpr int D_COL0 = 0, A_COL0 = MAX_ROWS;
 constexpr int SMEM_X = 0;
 constexpr int SMEM_RING = SMEM_X + ST * X_STAGE_BYTES;               // 196608
 constexpr int SMEM_BAR = SMEM_RING + NSTAGE_W * W_STAGE_BYTES;
-constexpr int NUM_BARS = 2 * NSTAGE_W + 2 * ST + 2;
+constexpr int NUM_BARS = 3 * NSTAGE_W + 2 * ST + 2;
 constexpr int SMEM_DYN = SMEM_BAR + NUM_BARS * 8 + 1024;             // + slack to align the base to 1024 bytes
 static_assert(A_COL0 + ST * STAGE_STEPS * 32 <= TMEM_COLS, "operand stages exceed tensor memory");
 static_assert(SMEM_DYN <= 227 * 1024, "shared memory");
@@ -79,11 +79,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + SMEM_BAR;
-    auto bar_full_w = [&](int s) { return bar0 + 8u * s; };                          // packed tiles landed
-    auto bar_empty_w = [&](int s) { return bar0 + 8u * (NSTAGE_W + s); };            // the groups have read them
-    auto bar_full = [&](int s) { return bar0 + 8u * (2 * NSTAGE_W + s); };           // stage s: X landed and A written
-    auto bar_empty = [&](int s) { return bar0 + 8u * (2 * NSTAGE_W + ST + s); };     // its MMAs retired
-    const uint32_t bar_d_full = bar0 + 8u * (2 * NSTAGE_W + 2 * ST);                 // an item's MMAs retired
+    // "packed tiles landed": two barriers per slot, for its even and its odd fills (see the dequantisers)
+    auto bar_full_w = [&](int s, int fill) { return bar0 + 8u * (2 * s + (fill & 1)); };
+    auto bar_empty_w = [&](int s) { return bar0 + 8u * (2 * NSTAGE_W + s); };        // the groups have read them
+    auto bar_full = [&](int s) { return bar0 + 8u * (3 * NSTAGE_W + s); };           // stage s: X landed and A written
+    auto bar_empty = [&](int s) { return bar0 + 8u * (3 * NSTAGE_W + ST + s); };     // its MMAs retired
+    const uint32_t bar_d_full = bar0 + 8u * (3 * NSTAGE_W + 2 * ST);                 // an item's MMAs retired
     const uint32_t bar_d_empty = bar_d_full + 8u;                                    // the accumulator was read out
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -98,7 +99,11 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < NSTAGE_W; ++s) { mbar_init(bar_full_w(s), 1); mbar_init(bar_empty_w(s), 4 * STAGE_STEPS); }
+        for (int s = 0; s < NSTAGE_W; ++s) {
+            mbar_init(bar_full_w(s, 0), 1);
+            mbar_init(bar_full_w(s, 1), 1);
+            mbar_init(bar_empty_w(s), 4 * STAGE_STEPS);
+        }
         // a stage is full when the X producer's expect-tx arrival, its bytes and the four warps of each
         // of its two k-tiles have arrived; one tcgen05.commit empties it
         for (int s = 0; s < ST; ++s) { mbar_init(bar_full(s), 1 + 4 * STAGE_STEPS); mbar_init(bar_empty(s), 1); }
@@ -123,14 +128,14 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
             const int valid = min(PANEL_TILES, NT - nt0);
             const uint8_t *src = prepacked + tile_offset(nt0 + min(lane, valid - 1), 0, KU);
             for (int q = 0; q < spi; ++q, ++gq) {
-                const int slot = gq % NSTAGE_W;
-                if (!mbar_wait_warp(bar_empty_w(slot), ((gq / NSTAGE_W) & 1) ^ 1, abort_flag, &g_status, 601)) goto done;
+                const int slot = gq % NSTAGE_W, fill = gq / NSTAGE_W;
+                if (!mbar_wait_warp(bar_empty_w(slot), (fill & 1) ^ 1, abort_flag, &g_status, 601)) goto done;
                 const uint32_t bytes = (uint32_t)(min(STAGE_STEPS, KU - q * STAGE_STEPS) * TILE_BYTES);
-                if (lane == 0) mbar_arrive_expect_tx(bar_full_w(slot), (uint32_t)valid * bytes);
+                if (lane == 0) mbar_arrive_expect_tx(bar_full_w(slot, fill), (uint32_t)valid * bytes);
                 __syncwarp();
                 if (lane < valid)
                     bulk_load(base + SMEM_RING + slot * W_STAGE_BYTES + lane * TILE_RUN_BYTES, src + (size_t)q * TILE_RUN_BYTES, bytes,
-                              bar_full_w(slot));
+                              bar_full_w(slot, fill));
             }
         }
     } else if (warp == WARP_X) {
@@ -245,14 +250,21 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
         for (int c = 0; c < 4; ++c) woff[c] = (uint32_t)(tile * TILE_RUN_BYTES + slot_of(g, c) * 16 + hi * 4);
         const uint32_t doff = (uint32_t)(tile * TILE_RUN_BYTES + TILE_QS_BYTES + g * 8 + hi * 2);
 
+        // A waiter on an mbarrier tells phases apart by parity only, so it must never test a barrier that
+        // is still a phase behind the one before its own.  "Stage empty": a group takes every fourth
+        // k-tile, so its previous wait (two stages back, hence the stage five back retired) implies that
+        // the slot's use six stages back has retired, MMAs retiring in order.  "Weights landed": a slot's
+        // even and odd fills complete on different barriers, so a test can only be fooled by the fill TWO
+        // before its own being outstanding; that fill was consumed before the producer issued the one in
+        // between, which it issued before the fill this group has already seen land (two stages back).
         int gbase = 0, itl = 0;                                   // global index of the item's first k-tile
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++itl, gbase += KU) {
             // this group's k-tiles of the item: those whose global index is grp modulo the number of groups
             int i = (grp - gbase % DEQ_GROUPS + DEQ_GROUPS) % DEQ_GROUPS;
             for (; i < KU; i += DEQ_GROUPS) {
                 const int gq = itl * spi + i / STAGE_STEPS, sub = i % STAGE_STEPS;
-                const int wslot = gq % NSTAGE_W, s = gq % ST;
-                if (!mbar_wait_warp(bar_full_w(wslot), (gq / NSTAGE_W) & 1, abort_flag, &g_status, 607)) goto done;
+                const int wslot = gq % NSTAGE_W, fill = gq / NSTAGE_W, s = gq % ST;
+                if (!mbar_wait_warp(bar_full_w(wslot, fill), (fill >> 1) & 1, abort_flag, &g_status, 607)) goto done;
                 if (!mbar_wait_warp(bar_empty(s), ((gq / ST) & 1) ^ 1, abort_flag, &g_status, 608)) goto done;
                 tc_fence_after();
                 const uint32_t wst = base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES;
