@@ -814,7 +814,8 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
 def run_probe(spec: str) -> None:
     """`--probe MxKxN`: six distinct weights, a warm-up launch and then one q4b_matmul launch each (fp16 activations), then the
     wait status; prints the average device time.  `--probe chain:L`: L layers of the 7B-shaped stage
-    list, three runs.  Small fixed cases for profiler captures."""
+    list, three runs.  `--probe quantize:NxK`: the packer on three fp16 [N, K] weights, both output
+    forms.  Small fixed cases for profiler captures."""
     from metalops_b200 import _cabi
     from metalops_b200 import quantization as Q
     dev = torch.device("cuda", 0)
@@ -834,6 +835,23 @@ def run_probe(spec: str) -> None:
         torch.cuda.synchronize(dev)
         print(json.dumps({"probe": spec, "launches": 3, "us_per_launch": e0.elapsed_time(e1) * 1e3 / 3,
                           "bytes_per_launch": sum(gemv_bytes(1, K, N) for _, K, N, _ in stack), "wait_status": Q.wait_status(dev)}))
+        return
+    if spec.startswith("quantize:"):
+        N, K = (int(v) for v in spec.split(":")[1].lower().split("x"))
+        g = torch.Generator(device=dev).manual_seed(4242)
+        ws = [(torch.randn(N, K, generator=g, device=dev) * 0.02).half() for _ in range(3)]
+        blocks = torch.empty((K // 32, N, 18), dtype=torch.uint8, device=dev)
+        pre = torch.empty(lib.q4b_prepacked_bytes(K, N), dtype=torch.uint8, device=dev)
+        sp = _cabi.stream_ptr(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        _cabi.check(lib.q4b_quantize(ws[0].data_ptr(), _cabi.F16, K, N, _cabi.LAYOUT_NK, blocks.data_ptr(), pre.data_ptr(), sp), "q4b_quantize")
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for w in ws:
+            _cabi.check(lib.q4b_quantize(w.data_ptr(), _cabi.F16, K, N, _cabi.LAYOUT_NK, blocks.data_ptr(), pre.data_ptr(), sp), "q4b_quantize")
+        e1.record()
+        torch.cuda.synchronize(dev)
+        print(json.dumps({"probe": spec, "launches": 3, "us_per_launch": e0.elapsed_time(e1) * 1e3 / 3}))
         return
     M, K, N = (int(v) for v in spec.lower().split("x"))
     g = torch.Generator(device=dev).manual_seed(4242)
@@ -860,7 +878,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--probe", default=None, metavar="MxKxN|chain:L", help="run one small case and exit (profiler captures)")
+    ap.add_argument("--probe", default=None, metavar="MxKxN|chain:L|quantize:NxK", help="run one small case and exit (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-gemm", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")

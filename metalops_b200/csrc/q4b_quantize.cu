@@ -4,7 +4,8 @@
 // (packages/metalcore/src/metalcore/quantization.py:328-371).  The reference evaluates
 // amax/7, w/d, +8 and round as separate tensor ops in the weight's dtype; for fp16 / bf16
 // each op computes in fp32 and rounds to the narrow type.  RoundTo<T> reproduces exactly that,
-// with IEEE division (__fdiv_rn) and ties-to-even rounding, so the bytes are identical.
+// with IEEE division (or an equivalent proven on every operand pair, see BlockDivider) and ties-to-even
+// rounding, so the bytes are identical.
 #include "q4b_common.cuh"
 
 namespace q4b {
@@ -47,6 +48,34 @@ __device__ __forceinline__ int round_clamp_q(float t) {
     return min(max(q, 0), 15);
 }
 
+// v / d as the reference's division gives it (IEEE, round to nearest), for the many values of one block.
+// For fp32 weights that is the division instruction sequence.  For fp16 / bf16 weights, whose d has at
+// most 11 significant bits, the quotient comes from the correctly rounded reciprocal of d, computed once
+// per block, and one fused correction step: q = v * r, e = fma(-q, d, v) (the exact remainder),
+// q + e * r.  The 4-bit result of the whole pipeline (round to T, + 8, round to T, round half to even,
+// clamp) is identical to the one through IEEE division for EVERY pair of fp16 and of bf16 operands with
+// 1e-30 <= d <= 1e30 and |v| <= 16.5 d: tests/exact_division_check.c enumerates them.  Outside that range
+// of d (bf16 scales near the fp32 denormals, an infinite block maximum) the division is used.
+template <typename T> struct BlockDivider {
+    float d, r;
+    bool fast;
+    __device__ __forceinline__ explicit BlockDivider(float d_) : d(d_), r(0.0f), fast(false) {
+        if constexpr (sizeof(T) == 2) {
+            fast = d_ >= 1e-30f && d_ <= 1e30f;
+            r = __frcp_rn(fast ? d_ : 1.0f);
+        }
+    }
+    __device__ __forceinline__ float operator()(float v) const {
+        if constexpr (sizeof(T) == 2) {
+            if (fast) {
+                const float q = __fmul_rn(v, r);
+                return __fmaf_rn(__fmaf_rn(-q, d, v), r, q);
+            }
+        }
+        return __fdiv_rn(v, d);
+    }
+};
+
 // Quantise the 32 values of one block.  Returns the fp16 scale bits and fills q[32].
 template <typename T>
 __device__ __forceinline__ uint16_t quantize_block(const float (&v)[QK], int (&q)[QK]) {
@@ -60,9 +89,10 @@ __device__ __forceinline__ uint16_t quantize_block(const float (&v)[QK], int (&q
     }
     float d = RoundTo<T>::r(__fdiv_rn(amax, 7.0f));   // quantization.py:341
     if (nan || !(d > 0.0f)) d = 1.0f;                 // quantization.py:342 (NaN amax fails d > 0)
+    const BlockDivider<T> div(d);
 #pragma unroll
     for (int i = 0; i < QK; i += 2) {
-        float t0 = __fdiv_rn(v[i], d), t1 = __fdiv_rn(v[i + 1], d);   // quantization.py:347, one rounding per op
+        float t0 = div(v[i]), t1 = div(v[i + 1]);     // quantization.py:347, one rounding per op
         round_pair<T>(t0, t1);
         t0 = __fadd_rn(t0, 8.0f);
         t1 = __fadd_rn(t1, 8.0f);
@@ -210,10 +240,10 @@ quantize_kn_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
 constexpr int QNK_KB = 8;
 constexpr int QNK_THREADS = TILE_N * QNK_KB * 4;
 
-constexpr int QNK_ITER = 1;            // groups of QNK_KB blocks per CTA (more than one measured slower: registers halve the CTAs per SM)
+constexpr int QNK_ITER = 2;            // groups of QNK_KB blocks per CTA: two loads in flight per thread at two CTAs per SM
 
 template <typename T>
-__global__ void __launch_bounds__(QNK_THREADS)
+__global__ void __launch_bounds__(QNK_THREADS, 2)
 quantize_nk_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__restrict__ blocks,
                    uint8_t *__restrict__ prepacked) {
     __shared__ __align__(16) uint8_t s_tile[QNK_KB / TILE_KB][TILE_BYTES];
@@ -283,9 +313,10 @@ quantize_nk_kernel(const T *__restrict__ w, int64_t K, int64_t N, uint8_t *__res
         if (ok) {
             dbits = __half_as_ushort(__float2half_rn(d));
             iw = 0;
+            const BlockDivider<T> div(d);
 #pragma unroll
             for (int i = 0; i < 8; i += 2) {
-                float t0 = __fdiv_rn(v[it][i], d), t1 = __fdiv_rn(v[it][i + 1], d);
+                float t0 = div(v[it][i]), t1 = div(v[it][i + 1]);
                 round_pair<T>(t0, t1);
                 t0 = __fadd_rn(t0, 8.0f);
                 t1 = __fadd_rn(t1, 8.0f);
