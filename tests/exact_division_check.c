@@ -51,7 +51,8 @@ int main(int argc, char **argv) {
             float q1 = fmaf(e, r, q);
             float ref = v / d;
             ++n;
-            if (memcmp(&q1, &ref, 4) != 0 && nib(q1, bf) != nib(ref, bf)) {    // equal quotients need no second look if (bad < 5) printf("mismatch v=%a d=%a fast=%a ref=%a\n", v, d, q1, ref); ++bad; }
+            /* equal quotients need no second look */
+            if (memcmp(&q1, &ref, 4) != 0 && nib(q1, bf) != nib(ref, bf)) { if (bad < 5) printf("mismatch v=%a d=%a fast=%a ref=%a\n", v, d, q1, ref); ++bad; }
         }
     }
     printf("%s: %ld pairs, %ld mismatches\n", bf ? "bf16" : "fp16", n, bad);
