@@ -195,6 +195,7 @@ def test_gemm_single_row_through_prefill_kernel(mo, cuda_dev):
     (1, 64, 16), (17, 32, 8), (129, 96, 48),          # one k-tile, half a k-tile, an odd number of k-tiles
     (256, 448, 520), (257, 192, 130), (300, 1056, 1000),   # row-tile boundaries: 256, 2 x 144, 2 x 160 rows
     (513, 2080, 272), (1000, 320, 4112), (2048, 4096, 384),
+    (200, 28672, 256),                                     # 224 stages per item
 ])
 def test_persistent_prefill_kernel_forced(mo, cuda_dev, M, K, N, xdtype):
     """The persistent kernel (items of 128 columns x up to 256 rows) at any M: stages of one and two
