@@ -176,7 +176,9 @@ Q4B_API int q4b_gemm_wt_addend(const void *x, int x_dtype, int64_t M, int64_t ld
  *                       and q4b_int4g_prepack_status (which synchronises the stream) reports it.
  * q4b_int4g_addend      addend[m, n] = sum_g corr[g, n] * sum_{k in g} x[m, k] + bias[n]  (fp32
  *                       [M, N]; bias fp32 [N] or NULL), to be passed to q4b_matmul_addend with the
- *                       prepacked tiles.  Any M.
+ *                       prepacked tiles.  Any M.  rowsums_ws: q4b_int4g_rowsums_bytes(M, K, group)
+ *                       bytes of device memory (the rows' group sums, [M, ceil(K/group)] fp32),
+ *                       written by a first kernel and read by the second.
  * q4b_int4g_matmul_generic  the same product straight from the [K/2, N] format for the shapes the
  *                       streaming tiles do not cover (K or group not a multiple of 32), as the
  *                       reference's Python loop accepts them (quantization.py:207-239): fp32
@@ -191,9 +193,10 @@ Q4B_API int q4b_int4g_prepack(const void *packed, const void *scales, const void
                               int sz_dtype, int64_t K, int64_t N, int64_t group,
                               void *prepacked_out, float *corr_out, void *stream);
 Q4B_API int q4b_int4g_prepack_status(void *stream, int *out_of_range);
+Q4B_API size_t q4b_int4g_rowsums_bytes(int64_t M, int64_t K, int64_t group);
 Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr,
-                             const float *bias, int64_t K, int64_t N, int64_t group, float *addend_out,
-                             void *stream);
+                             const float *bias, int64_t K, int64_t N, int64_t group, float *rowsums_ws,
+                             float *addend_out, void *stream);
 Q4B_API int q4b_int4g_matmul_generic(const void *x, int x_dtype, int64_t M, int64_t ldx,
                                      const void *packed, const void *scales, const void *zeros,
                                      int sz_dtype, int64_t K, int64_t N, int64_t group, void *y,

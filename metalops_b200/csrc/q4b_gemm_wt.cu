@@ -197,6 +197,14 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++itl) {
             const int row0 = (item / panels) * rows;
             const int n = (item % panels) * PANEL_N + quad * 32 + lane;
+            if (addend != nullptr && ld_add != 0 && lane == 0) {
+                // the item's main loop takes tens of microseconds: ask L2 for this warp's part of the addend
+                // tile (a 128-byte line per row) now, so that the drain does not wait for DRAM
+                const int nq = (item % panels) * PANEL_N + quad * 32;
+                if (nq < N)
+                    for (int rr = ch0 * 32; rr < min(ch1 * 32, rows) && row0 + rr < M; ++rr)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(addend + (size_t)(row0 + rr) * ld_add + nq));
+            }
             if (!mbar_wait_warp(bar_d_full, (uint32_t)(itl & 1), abort_flag, &g_status, 606)) goto done;
             tc_fence_after();
 #pragma unroll 1
@@ -219,14 +227,17 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                                 else *yp = __half_as_ushort(__float2half_rn(f));
                             }
                         } else {
-                            const float *ap = addend != nullptr ? addend + (size_t)m0 * ld_add + n : nullptr;
+                            // the addend's sixteen values first, all loads in flight together: interleaved
+                            // with the stores they would wait for one another (the stores may alias them)
                             const int jn = min(16, M - m0);
+                            float a[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                a[j] = (addend != nullptr && j < jn) ? __ldg(addend + (size_t)(m0 + j) * ld_add + n) : 0.0f;
 #pragma unroll
                             for (int j = 0; j < 16; ++j, yp += ldy) {
                                 if (j < jn) {
-                                    float f = __uint_as_float(v[u][j]);
-                                    if (ap != nullptr) f += ap[(size_t)j * ld_add];      // fp32 term added before the one rounding
-                                    f = apply_act(f, act);
+                                    const float f = apply_act(__uint_as_float(v[u][j]) + a[j], act);    // fp32 term added before the one rounding
                                     if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
                                     else *yp = __half_as_ushort(__float2half_rn(f));
                                 }

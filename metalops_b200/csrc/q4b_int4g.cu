@@ -139,31 +139,91 @@ int4g_corr_kernel(const TS *__restrict__ scales, const TS *__restrict__ zeros, i
     corr[i] = __fsub_rn(__fmul_rn(8.0f, d), __fmul_rn(z, s));
 }
 
-// addend[m, n] = sum_g corr[g, n] * (sum of x[m, k] over group g) (+ bias[n]).  A CTA takes whole
-// rows (grid-stride over m): the row's group sums are built once, every warp summing whole groups
-// with coalesced loads and a fixed-order shuffle reduction, then the columns are swept.
+// The group-wise format's zero-point term, addend[m, n] = sum_g corr[g, n] * (sum of x[m, k] over group g)
+// (+ bias[n]), is a product of rank G = K / group.  Two kernels:
+//   int4g_rowsum_kernel  R[m, g]: a warp per (row, group), coalesced loads, fixed-order shuffle reduction;
+//                        X is read once.
+//   int4g_addend_kernel  a CTA takes 512 columns x 32 rows: a thread owns two columns, their corr[g, n]
+//                        values arrive 16 groups at a time (coalesced over the CTA), the rows' group sums
+//                        are broadcast from shared memory (one 16-byte read feeds eight FMAs), 2 x 32
+//                        accumulators per thread, coalesced fp32 stores.  corr is re-read once per row
+//                        tile, from L2.
 template <typename TX>
 __global__ void __launch_bounds__(256)
-int4g_addend_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, const float *__restrict__ corr,
-                    const float *__restrict__ bias, int64_t K, int64_t N, int64_t group, int G, float *__restrict__ addend) {
-    extern __shared__ float xs[];
+int4g_rowsum_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t K, int64_t group, int G, float *__restrict__ rowsums) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+    const int64_t pairs = M * G;
+    for (int64_t p = (int64_t)blockIdx.x * 8 + warp; p < pairs; p += (int64_t)gridDim.x * 8) {
+        const int64_t m = p / G;
+        const int g = (int)(p % G);
         const TX *xr = x + m * ldx;
-        __syncthreads();
-        for (int g = warp; g < G; g += 8) {
-            const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
-            float s = 0.0f;
-            for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
+        const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
+        float s = 0.0f;
+        for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) xs[g] = s;
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) rowsums[p] = s;
+    }
+}
+
+constexpr int ADD_ROWS = 32;       // rows per CTA of the addend kernel: corr is re-read from L2 once per this many rows
+constexpr int ADD_COLS = 512;      // columns per CTA: two per thread, so a broadcast read of four group sums feeds eight FMAs
+constexpr int ADD_GCHUNK = 16;     // groups per pass
+
+__global__ void __launch_bounds__(256, 2)
+int4g_addend_kernel(const float *__restrict__ rowsums, int64_t M, const float *__restrict__ corr,
+                    const float *__restrict__ bias, int64_t N, int G, float *__restrict__ addend) {
+    __shared__ __align__(16) float rs[ADD_ROWS][ADD_GCHUNK];
+    const int64_t n = (int64_t)blockIdx.x * ADD_COLS + 2 * threadIdx.x;          // this thread's columns: n, n + 1
+    const int64_t m0 = (int64_t)blockIdx.y * ADD_ROWS;
+    const int nrows = (int)min((int64_t)ADD_ROWS, M - m0);
+    const bool ok0 = n < N, ok1 = n + 1 < N;
+    const bool pair = ok1 && (N % 2 == 0);                                        // both columns, 8-byte aligned
+    float acc0[ADD_ROWS], acc1[ADD_ROWS];
+    const float b0 = (bias != nullptr && ok0) ? bias[n] : 0.0f, b1 = (bias != nullptr && ok1) ? bias[n + 1] : 0.0f;
+#pragma unroll
+    for (int r = 0; r < ADD_ROWS; ++r) { acc0[r] = b0; acc1[r] = b1; }
+    for (int g0 = 0; g0 < G; g0 += ADD_GCHUNK) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < ADD_ROWS * ADD_GCHUNK; i += 256) {
+            const int r = i / ADD_GCHUNK, g = g0 + i % ADD_GCHUNK;
+            rs[r][i % ADD_GCHUNK] = (r < nrows && g < G) ? rowsums[(m0 + r) * G + g] : 0.0f;
+        }
+        float c0[ADD_GCHUNK], c1[ADD_GCHUNK];
+#pragma unroll
+        for (int j = 0; j < ADD_GCHUNK; ++j) {
+            const float *cp = corr + (int64_t)(g0 + j) * N + n;
+            if (g0 + j < G && pair) {
+                const float2 v = *reinterpret_cast<const float2 *>(cp);
+                c0[j] = v.x;
+                c1[j] = v.y;
+            } else {
+                c0[j] = (g0 + j < G && ok0) ? cp[0] : 0.0f;
+                c1[j] = (g0 + j < G && ok1) ? cp[1] : 0.0f;
+            }
         }
         __syncthreads();
-        for (int64_t n = threadIdx.x; n < N; n += 256) {
-            float acc = bias != nullptr ? bias[n] : 0.0f;
-            for (int g = 0; g < G; ++g) acc = fmaf(corr[(int64_t)g * N + n], xs[g], acc);
-            addend[m * N + n] = acc;
+#pragma unroll
+        for (int r = 0; r < ADD_ROWS; ++r) {
+#pragma unroll
+            for (int j = 0; j < ADD_GCHUNK; j += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(&rs[r][j]);      // the same address in every lane: a broadcast
+                acc0[r] = fmaf(c0[j], v.x, acc0[r]);      acc1[r] = fmaf(c1[j], v.x, acc1[r]);
+                acc0[r] = fmaf(c0[j + 1], v.y, acc0[r]);  acc1[r] = fmaf(c1[j + 1], v.y, acc1[r]);
+                acc0[r] = fmaf(c0[j + 2], v.z, acc0[r]);  acc1[r] = fmaf(c1[j + 2], v.z, acc1[r]);
+                acc0[r] = fmaf(c0[j + 3], v.w, acc0[r]);  acc1[r] = fmaf(c1[j + 3], v.w, acc1[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ADD_ROWS; ++r) {
+        if (r < nrows) {
+            float *op = addend + (m0 + r) * N + n;
+            if (pair) *reinterpret_cast<float2 *>(op) = make_float2(acc0[r], acc1[r]);
+            else {
+                if (ok0) op[0] = acc0[r];
+                if (ok1) op[1] = acc1[r];
+            }
         }
     }
 }
@@ -255,21 +315,39 @@ extern "C" int q4b_int4g_prepack(const void *packed, const void *scales, const v
     }
 }
 
+extern "C" size_t q4b_int4g_rowsums_bytes(int64_t M, int64_t K, int64_t group) {
+    if (M < 1 || K < 1 || group < 1) return 0;
+    return (size_t)M * (size_t)ceil_div(K, group) * sizeof(float);
+}
+
 extern "C" int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr, const float *bias,
-                                int64_t K, int64_t N, int64_t group, float *addend_out, void *stream) {
-    if (x == nullptr || corr == nullptr || addend_out == nullptr) return Q4B_ERR_ARG;
+                                int64_t K, int64_t N, int64_t group, float *rowsums_ws, float *addend_out, void *stream) {
+    if (x == nullptr || corr == nullptr || addend_out == nullptr || rowsums_ws == nullptr) return Q4B_ERR_ARG;
     if (M < 1 || ldx < K) return Q4B_ERR_ARG;
     if (int rc = check_g(K, N, group)) return rc;
     const int64_t G = ceil_div(K, group);
-    if (G > 8192) return Q4B_ERR_TOO_LARGE;
-    const unsigned grid = (unsigned)(M < 4096 ? M : 4096);
-    const size_t smem = (size_t)G * sizeof(float);
+    if (ceil_div(M, ADD_ROWS) > 65535) {
+        // more row tiles than grid.y holds: in slices of 65535 tiles
+        const int64_t step = (int64_t)65535 * ADD_ROWS;
+        for (int64_t m0 = 0; m0 < M; m0 += step) {
+            const int64_t rows = M - m0 < step ? M - m0 : step;
+            if (int rc = q4b_int4g_addend((const uint8_t *)x + (size_t)m0 * ldx * 2, x_dtype, rows, ldx, corr, bias, K, N, group,
+                                          rowsums_ws + m0 * G, addend_out + m0 * N, stream))
+                return rc;
+        }
+        return Q4B_OK;
+    }
+    const int64_t pairs = M * G;
+    const unsigned grid1 = (unsigned)(ceil_div(pairs, 8) < 16384 ? ceil_div(pairs, 8) : 16384);
     cudaStream_t st = (cudaStream_t)stream;
     switch (x_dtype) {
-        case Q4B_F16: int4g_addend_kernel<__half><<<grid, 256, smem, st>>>((const __half *)x, M, ldx, corr, bias, K, N, group, (int)G, addend_out); break;
-        case Q4B_BF16: int4g_addend_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>((const __nv_bfloat16 *)x, M, ldx, corr, bias, K, N, group, (int)G, addend_out); break;
+        case Q4B_F16: int4g_rowsum_kernel<__half><<<grid1, 256, 0, st>>>((const __half *)x, M, ldx, K, group, (int)G, rowsums_ws); break;
+        case Q4B_BF16: int4g_rowsum_kernel<__nv_bfloat16><<<grid1, 256, 0, st>>>((const __nv_bfloat16 *)x, M, ldx, K, group, (int)G, rowsums_ws); break;
         default: return Q4B_ERR_DTYPE;
     }
+    Q4B_LAUNCH_CHECK();
+    dim3 grid2((unsigned)ceil_div(N, ADD_COLS), (unsigned)ceil_div(M, ADD_ROWS));
+    int4g_addend_kernel<<<grid2, 256, 0, st>>>(rowsums_ws, M, corr, bias, N, (int)G, addend_out);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }

@@ -380,13 +380,15 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
     if M == 0:
         return torch.empty((0, N), dtype=in_dtype, device=x.device)
     addend = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    lib = _cabi.load()
+    rowsums = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, pre.group_size) // 4, dtype=torch.float32, device=x.device)
     b32 = None
     if bias is not None:
         b32 = bias.to(device=x.device, dtype=torch.float32).contiguous()
     with torch.cuda.device(x.device):
-        rc = _cabi.load().q4b_int4g_addend(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.corr.data_ptr(),
-                                           b32.data_ptr() if b32 is not None else None, K, N, pre.group_size,
-                                           addend.data_ptr(), _cabi.stream_ptr(x.device))
+        rc = lib.q4b_int4g_addend(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.corr.data_ptr(),
+                                  b32.data_ptr() if b32 is not None else None, K, N, pre.group_size,
+                                  rowsums.data_ptr(), addend.data_ptr(), _cabi.stream_ptr(x.device))
     _cabi.check(rc, "matmul_int4")
     y = _matmul_prepacked(x, pre.tiles, addend=addend, flags=_ACT_FLAGS[activation])
     return y.float() if in_dtype == torch.float32 else y
