@@ -69,7 +69,9 @@ template <bool BF16> __device__ __forceinline__ uint32_t scale_pair(uint16_t dbi
     }
 }
 
-template <bool BF16>
+// GENERAL: the epilogue adds the fp32 addend and applies the activation; without it (its own instantiation,
+// so that the common case keeps its registers) it only converts and stores.
+template <bool BF16, bool GENERAL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked, int M, int64_t K, int64_t N,
                uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add, int rows, int act) {
@@ -191,13 +193,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
         // ---------------- epilogue: two warps per lane quadrant, half of the rows each ----------------
         const int quad = warp & 3, half = (warp - WARP_EPI0) >> 2;
         const uint32_t lane_taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const bool plain = addend == nullptr && act == 0;
         const int nch = (rows + 31) / 32, ch0 = half * ((nch + 1) / 2), ch1 = half == 0 ? (nch + 1) / 2 : nch;   // chunks of 32 rows
         int itl = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++itl) {
             const int row0 = (item / panels) * rows;
             const int n = (item % panels) * PANEL_N + quad * 32 + lane;
-            if (addend != nullptr && ld_add != 0 && lane == 0) {
+            if (GENERAL && addend != nullptr && ld_add != 0 && lane == 0) {
                 // the item's main loop takes tens of microseconds: ask L2 for this warp's part of the addend
                 // tile (a 128-byte line per row) now, so that the drain does not wait for DRAM
                 const int nq = (item % panels) * PANEL_N + quad * 32;
@@ -218,13 +219,23 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                     const int m0 = row0 + ch * 32 + u * 16;
                     if (n < N && m0 < M && ch * 32 + u * 16 < rows) {
                         uint16_t *yp = y + (size_t)m0 * ldy + n;
-                        if (plain && m0 + 16 <= M) {
+                        if (!GENERAL && m0 + 16 <= M) {
                             // the common case costs a conversion, a store and an address step per element
 #pragma unroll
                             for (int j = 0; j < 16; ++j, yp += ldy) {
                                 const float f = __uint_as_float(v[u][j]);
                                 if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
                                 else *yp = __half_as_ushort(__float2half_rn(f));
+                            }
+                        } else if constexpr (!GENERAL) {
+                            const int jn = min(16, M - m0);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j, yp += ldy) {
+                                if (j < jn) {
+                                    const float f = __uint_as_float(v[u][j]);
+                                    if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                                    else *yp = __half_as_ushort(__float2half_rn(f));
+                                }
                             }
                         } else {
                             // the addend's sixteen values first, all loads in flight together: interleaved
@@ -352,7 +363,7 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-template <bool BF16>
+template <bool BF16, bool GENERAL>
 static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t K, int64_t N, void *y, int64_t ldy,
                   const float *addend, int64_t ld_add, int rows, int act, int sms, cudaStream_t st) {
     {   // opt in to the large dynamic shared memory once per device and instantiation
@@ -362,13 +373,13 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t
         Q4B_CUDA_TRY(cudaGetDevice(&dev));
         std::lock_guard<std::mutex> attr_lock(attr_mu);
         if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_wt_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+            Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_wt_kernel<BF16, GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
     const int64_t items = ceil_div(tiles_n(N), PANEL_TILES) * ceil_div(M, rows);
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    gemm_wt_kernel<BF16><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, M, K, N, (uint16_t *)y, ldy, addend,
+    gemm_wt_kernel<BF16, GENERAL><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, M, K, N, (uint16_t *)y, ldy, addend,
                                                         ld_add, rows, act);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
@@ -401,8 +412,11 @@ int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prep
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return Q4B_ERR_ARG;
     const int act = act_of_flags(flags);
-    return bf16 ? gemmwt::launch<true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st)
-                : gemmwt::launch<false>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st);
+    if (addend != nullptr || act != 0)
+        return bf16 ? gemmwt::launch<true, true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st)
+                    : gemmwt::launch<false, true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st);
+    return bf16 ? gemmwt::launch<true, false>(tmap, prepacked, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st)
+                : gemmwt::launch<false, false>(tmap, prepacked, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st);
 }
 
 // read and clear this file's wait status (host side; the caller has synchronised the stream)
