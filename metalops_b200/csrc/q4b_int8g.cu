@@ -88,9 +88,10 @@ quantize_ggml_kernel(const T *__restrict__ w, int64_t K, int64_t N, int nk_layou
 
 // ---- group-wise INT8 matmul ---------------------------------------------------------------------
 constexpr int I8_THREADS = 256;                  // 8 warps split k
-constexpr int I8_COLS = 128;                     // columns per CTA: 4 per lane
+constexpr int I8_COLS = 32;                      // columns per CTA: 4 per lane, 8 lanes across
 constexpr int I8_ROWS = 8;                       // rows of X per CTA
-constexpr int I8_KC = 256;                       // k per shared-memory slice of X
+constexpr int I8_KC = 512;                       // k per shared-memory slice of X
+constexpr int I8_UNROLL = 8;                     // weight loads in flight per lane
 
 template <typename T> __device__ __forceinline__ T out_cast(float v);
 template <> __device__ __forceinline__ __half out_cast<__half>(float v) { return __float2half_rn(v); }
@@ -104,14 +105,22 @@ __device__ __forceinline__ float byte_to_float(uint32_t w_xor80, int sel) {
 
 // NIBBLES: wq is the group-wise INT4 format instead, uint8 [K/2, N], byte r of a column = value 2r in
 // its low and value 2r + 1 in its high nibble (values 0..15).
+//
+// A CTA takes 32 columns and up to 8 rows of X.  A warp load covers four consecutive k rows of the
+// weight, 32 bytes (one sector) of each: lane = (k row of the four, column quad).  The eight warps take
+// the k rows 4w..4w+3, + 32, + 64, ...; eight loads per lane are issued before their values are used.
+// (scale, zero) of the lane's columns are reloaded only when its k crosses into another group.  At the
+// end the four k rows of a warp are summed by shuffles and the eight warps through shared memory, both
+// in a fixed order.
 template <typename TX, typename TS, bool NIBBLES>
-__global__ void __launch_bounds__(I8_THREADS)
+__global__ void __launch_bounds__(I8_THREADS, 3)
 int8g_matmul_kernel(const TX *__restrict__ x, int M, int64_t ldx, const int8_t *__restrict__ wq, const TS *__restrict__ scales,
                     const TS *__restrict__ zeros, int64_t K, int64_t N, int group, TX *__restrict__ y, int64_t ldy) {
-    __shared__ float xs[I8_ROWS][I8_KC];
+    __shared__ __align__(16) float xs[I8_KC][I8_ROWS];       // [k][row]: a k's eight rows are two 16-byte reads
     __shared__ float red[I8_THREADS / 32][I8_ROWS][I8_COLS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t n0 = (int64_t)blockIdx.x * I8_COLS + lane * 4;
+    const int cq = lane & 7, ks = lane >> 3;
+    const int64_t n0 = (int64_t)blockIdx.x * I8_COLS + cq * 4;
     const int m0 = (int)blockIdx.y * I8_ROWS;
     const int rows = min(I8_ROWS, M - m0);
     const bool vec = (N % 4 == 0) && n0 + 3 < N;
@@ -120,59 +129,100 @@ int8g_matmul_kernel(const TX *__restrict__ x, int M, int64_t ldx, const int8_t *
     for (int r = 0; r < I8_ROWS; ++r)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+    float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, zr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int64_t g_end = 0;                                  // the cached (scale, zero) hold for k < g_end
 
     for (int64_t kc = 0; kc < K; kc += I8_KC) {
         const int klen = (int)min((int64_t)I8_KC, K - kc);
         __syncthreads();
         for (int i = threadIdx.x; i < I8_ROWS * I8_KC; i += I8_THREADS) {
-            const int r = i / I8_KC, k = i % I8_KC;
-            xs[r][k] = (r < rows && k < klen) ? (float)x[(size_t)(m0 + r) * ldx + kc + k] : 0.0f;
+            const int r = i / I8_KC, k = i % I8_KC;                    // consecutive threads read consecutive k of a row
+            xs[k][r] = (r < rows && k < klen) ? (float)x[(size_t)(m0 + r) * ldx + kc + k] : 0.0f;
         }
         __syncthreads();
-        // warp w takes rows k = w, w + 8, ... of the slice; a group never straddles what one
-        // (scale, zero) pair covers because they are applied per k
-        for (int k = warp; k < klen; k += I8_THREADS / 32) {
-            const int64_t kk = kc + k;
-            const int64_t gi = kk / group;
-            float wv[4];
-            if constexpr (NIBBLES) {
-                const uint8_t *row = reinterpret_cast<const uint8_t *>(wq) + (kk >> 1) * N;
-                const int sh = (int)(kk & 1) * 4;
-                if (vec) {
-                    const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(row + n0));
+        for (int t0 = 0; t0 < I8_KC / 32; t0 += I8_UNROLL) {
+            if (t0 * 32 >= klen) break;                 // uniform over the CTA
+            uint32_t word[I8_UNROLL];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) wv[j] = (float)((word >> (8 * j + sh)) & 0xFu);
-                } else {
+            for (int u = 0; u < I8_UNROLL; ++u) {
+                const int k = warp * 4 + ks + 32 * (t0 + u);
+                const int64_t kk = kc + k;
+                word[u] = 0;
+                if (k < klen) {
+                    const uint8_t *row = NIBBLES ? reinterpret_cast<const uint8_t *>(wq) + (kk >> 1) * N
+                                                 : reinterpret_cast<const uint8_t *>(wq) + kk * N;
+                    if (vec) {
+                        word[u] = __ldg(reinterpret_cast<const uint32_t *>(row + n0));
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) wv[j] = n0 + j < N ? (float)((row[n0 + j] >> sh) & 0xF) : 0.0f;
+                        for (int j = 0; j < 4; ++j)
+                            if (n0 + j < N) word[u] |= (uint32_t)row[n0 + j] << (8 * j);
+                    }
                 }
-            } else if (vec) {
-                const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(wq + kk * N + n0)) ^ 0x80808080u;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) wv[j] = byte_to_float(word, j);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) wv[j] = n0 + j < N ? (float)wq[kk * N + n0 + j] : 0.0f;
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const bool ok = n0 + j < N;
-                const float s = ok ? (float)scales[gi * N + n0 + j] : 0.0f;
-                const float z = ok ? (float)zeros[gi * N + n0 + j] : 0.0f;
-                wv[j] = (wv[j] - z) * s;                       // (w_q - zero) * scale, as the reference
-            }
+            for (int u = 0; u < I8_UNROLL; ++u) {
+                const int k = warp * 4 + ks + 32 * (t0 + u);
+                if (k < klen) {
+                    const int64_t kk = kc + k;
+                    if (kk >= g_end) {                  // another group: its scale and zero point
+                        const int64_t gi = kk / group;
+                        g_end = (gi + 1) * (int64_t)group;
 #pragma unroll
-            for (int r = 0; r < I8_ROWS; ++r) {
-                const float xv = xs[r][k];
+                        for (int j = 0; j < 4; ++j) {
+                            const bool ok = n0 + j < N;
+                            sc[j] = ok ? (float)scales[gi * N + n0 + j] : 0.0f;
+                            zr[j] = ok ? (float)zeros[gi * N + n0 + j] : 0.0f;
+                        }
+                    }
+                    float wv[4];
+                    if constexpr (NIBBLES) {
+                        const int sh = (int)(kk & 1) * 4;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[r][j] = fmaf(xv, wv[j], acc[r][j]);
+                        for (int j = 0; j < 4; ++j) wv[j] = (float)((word[u] >> (8 * j + sh)) & 0xFu);
+                    } else {
+                        const uint32_t wx = word[u] ^ 0x80808080u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) wv[j] = byte_to_float(wx, j);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) wv[j] = (wv[j] - zr[j]) * sc[j];      // (w_q - zero) * scale, as the reference
+                    const float4 xa = *reinterpret_cast<const float4 *>(&xs[k][0]);
+                    const float xr[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[0][j] = fmaf(xr[0], wv[j], acc[0][j]);
+                    if (rows > 1) {                                 // uniform over the CTA: a single row is the common case
+#pragma unroll
+                        for (int r = 1; r < 4; ++r)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) acc[r][j] = fmaf(xr[r], wv[j], acc[r][j]);
+                    }
+                    if (rows > 4) {
+                        const float4 xb = *reinterpret_cast<const float4 *>(&xs[k][4]);
+                        const float xq[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                        for (int r = 0; r < 4; ++r)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) acc[4 + r][j] = fmaf(xq[r], wv[j], acc[4 + r][j]);
+                    }
+                }
             }
         }
     }
+    // the warp's four k rows: lanes l, l + 8, l + 16, l + 24 hold the same columns
 #pragma unroll
     for (int r = 0; r < I8_ROWS; ++r)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) red[warp][r][lane * 4 + j] = acc[r][j];
+        for (int j = 0; j < 4; ++j) {
+            acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 8);
+            acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], 16);
+        }
+    if (ks == 0) {
+#pragma unroll
+        for (int r = 0; r < I8_ROWS; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red[warp][r][cq * 4 + j] = acc[r][j];
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < I8_ROWS * I8_COLS; i += I8_THREADS) {
         const int r = i / I8_COLS, cidx = i % I8_COLS;
