@@ -350,7 +350,7 @@ def run_ours(args) -> None:
     if not args.skip_e2e:
         e2e = bench_e2e(dev, stream, lib, stack, xs, chain_ready, step_bytes, world, args, barrier)
 
-    gemm = quant = sweeps = batch = sharded = None
+    gemm = quant = sweeps = batch = sharded = int4g = None
     if not args.skip_gemm:
         gemm = bench_gemm(dev, stream, lib, peaks, traffic, local)
     if rank == 0 and not args.skip_extra:
@@ -361,6 +361,7 @@ def run_ours(args) -> None:
     torch.cuda.empty_cache()
     if rank == 0 and not args.skip_extra:
         sweeps = bench_sweeps(dev, stream, lib, peaks)
+        int4g = bench_groupwise_int4(dev, stream, lib, peaks)
     if not args.skip_extra:
         sharded = bench_sharded(dev, stream, lib, rank, world, peaks)
 
@@ -392,7 +393,8 @@ def run_ours(args) -> None:
             "decode_variants": extras,
             "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
         }
-        for key, val in (("gemm", gemm), ("quantize", quant), ("sweeps", sweeps), ("decode_batch", batch), ("sharded", sharded)):
+        for key, val in (("gemm", gemm), ("quantize", quant), ("sweeps", sweeps), ("decode_batch", batch), ("groupwise_int4", int4g),
+                         ("sharded", sharded)):
             if val is not None:
                 out[key] = val
         if not args.skip_cpu:
@@ -679,6 +681,51 @@ def bench_sweeps(dev, stream, lib, peaks):
         out[label] = res
         del pres
         torch.cuda.empty_cache()
+    return out
+
+
+def bench_groupwise_int4(dev, stream, lib, peaks):
+    """The group-wise asymmetric INT4 format (K=4096, N=14336, group 128, bf16 activations) through the
+    C ABI with every buffer allocated once: the zero-point term (q4b_int4g_addend: group sums, then the
+    rank-G product into an [M, N] fp32 addend) followed by q4b_matmul_addend on the streaming tiles, at
+    M = 1 and M = 2048; next to it the same product on the tiles alone.  Four weights rotate."""
+    import metalops_b200 as mo
+    from metalops_b200 import _cabi
+    from metalops_b200 import quantization as Q
+    K, N, G = 4096, 14336, 128
+    g = torch.Generator(device=dev).manual_seed(1006)
+    sets = []
+    for _ in range(4):
+        w = (torch.randn(K, N, generator=g, device=dev) * 0.02).half()
+        sets.append(Q.prepack_int4(*mo.quantize_int4(w, G), G))
+        del w
+    out = {"config": f"K={K} N={N} group {G}, bf16 activations, fp32 [M, N] addend"}
+    for M in (1, 2048):
+        x = torch.randn(M, K, generator=g, device=dev).bfloat16()
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        adds = [torch.empty((M, N), dtype=torch.float32, device=dev) for _ in sets]
+        rs = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, G) // 4, dtype=torch.float32, device=dev)
+
+        def full(i, M=M, x=x, y=y, adds=adds, rs=rs):
+            sp = torch.cuda.current_stream(dev).cuda_stream
+            p = sets[i % 4]
+            rc = lib.q4b_int4g_addend(x.data_ptr(), _cabi.BF16, M, K, p.corr.data_ptr(), None, K, N, G, rs.data_ptr(),
+                                      adds[i % 4].data_ptr(), sp)
+            rc = rc or lib.q4b_matmul_addend(x.data_ptr(), _cabi.BF16, M, K, p.tiles.data.data_ptr(), K, N, adds[i % 4].data_ptr(), N,
+                                             y.data_ptr(), N, 0, sp)
+            if rc:
+                _cabi.check(rc, "group-wise INT4 matmul")
+
+        def tiles_only(i, M=M, x=x, y=y):
+            rc = lib.q4b_matmul_addend(x.data_ptr(), _cabi.BF16, M, K, sets[i % 4].tiles.data.data_ptr(), K, N, None, 0, y.data_ptr(), N, 0,
+                                       torch.cuda.current_stream(dev).cuda_stream)
+            if rc:
+                _cabi.check(rc, "q4b_matmul_addend")
+
+        us_full = time_launches(stream, full, 8) * 1e3
+        us_tiles = time_launches(stream, tiles_only, 8) * 1e3
+        out[f"m{M}"] = {"us_per_product": us_full, "us_tiles_only": us_tiles, "tflops": 2.0 * M * K * N / us_full / 1e6,
+                        "weight_gbps": gemv_bytes(M, K, N) / us_full / 1e3}
     return out
 
 
