@@ -232,3 +232,26 @@ def test_int4_linear_default_runs_the_fused_kernels(mo, cuda_dev):
     assert orc.rel_l2(y[:64], lin(x[:64].float())) <= 0.2
     ql.dequantize()
     assert "fast_fp16" in ql.extra_repr()
+
+
+def test_addend_many_rows_and_ragged_tiles(mo, cuda_dev):
+    """q4b_int4g_addend through the C ABI: more row tiles than a grid dimension holds (the entry point
+    slices them), a last tile of few rows, odd N (scalar loads and stores), two passes over the groups."""
+    from metalops_b200 import _cabi
+    lib = _cabi.load()
+    g = torch.Generator().manual_seed(77)
+    for M, K, N, group in ((2_097_153, 64, 3, 32), (37, 2304, 515, 128), (1, 4096, 1000, 32)):
+        G = K // group
+        x = torch.randn(M, K, generator=g).half().to(cuda_dev)
+        corr = torch.randn(G, N, generator=g).to(cuda_dev)
+        bias = torch.randn(N, generator=g).to(cuda_dev)
+        out = torch.empty((M, N), dtype=torch.float32, device=cuda_dev)
+        ws = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, group) // 4, dtype=torch.float32, device=cuda_dev)
+        assert ws.numel() == M * G
+        rc = lib.q4b_int4g_addend(x.data_ptr(), _cabi.F16, M, K, corr.data_ptr(), bias.data_ptr(), K, N, group, ws.data_ptr(),
+                                  out.data_ptr(), _cabi.stream_ptr(cuda_dev))
+        assert rc == 0
+        torch.cuda.synchronize()
+        ref = x.float().view(M, G, group).sum(-1) @ corr + bias
+        assert torch.allclose(out, ref, rtol=1e-4, atol=1e-4), (M, K, N, float((out - ref).abs().max()))
+    assert lib.q4b_int4g_addend(x.data_ptr(), _cabi.F16, 1, 4096, corr.data_ptr(), None, 4096, 1000, 32, None, out.data_ptr(), None) == _cabi.ERR_ARG
