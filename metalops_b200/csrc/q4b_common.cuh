@@ -131,6 +131,17 @@ __device__ __forceinline__ void dequant_word_biased(uint32_t w, uint32_t (&h)[4]
     }
 }
 
+// A block's fp16 scale as a pair in the activations' type (bf16: rounded once from fp16).
+template <bool BF16> __device__ __forceinline__ uint32_t scale_pair(uint16_t dbits) {
+    if constexpr (BF16) {
+        __nv_bfloat16 b = __float2bfloat16_rn(__half2float(__ushort_as_half(dbits)));
+        uint32_t u = __bfloat16_as_ushort(b);
+        return u | (u << 16);
+    } else {
+        return (uint32_t)dbits | ((uint32_t)dbits << 16);
+    }
+}
+
 // ---- epilogue activation (flags Q4B_FLAG_ACT_*: 0 none, 1 SiLU, 2 tanh-GELU), applied to the fp32 sum ----
 // Formulas of the reference's fused kernels (quant_kernels.metal:997, 1125-1131).
 __host__ __device__ inline int act_of_flags(int flags) { return (flags >> 3) & 3; }

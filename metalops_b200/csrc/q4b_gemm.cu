@@ -7,7 +7,11 @@
 //   M <= 128   q4b_gemm_tmem.cu: a CTA per 128-column panel and k range (clusters split k), whose cost per
 //              k-tile does not depend on M, unless the weight has more panels than two per SM;
 //   otherwise  q4b_gemm_wt.cu: persistent CTAs over items of 128 columns x up to 256 rows x all of k.
-#include "q4b_common.cuh"
+#include <cuda.h>
+
+#include <mutex>
+
+#include "q4b_sm100_ptx.cuh"
 
 namespace q4b {
 
@@ -21,6 +25,38 @@ int gemm_tmem_wait_status(int *value);
 int gemm_wt_wait_status(int *value);
 namespace chain { int wait_status(int *value); }
 int selftest_wait_status(int *value);
+
+// cuTensorMapEncodeTiled through the runtime, so the library has no link dependency on libcuda
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+int encode_x_tensor_map(CUtensorMap *map, const void *x, int bf16, int64_t M, int64_t K, int64_t ldx, int rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (enc == nullptr) return Q4B_ERR_CUDA;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x),
+                           dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? Q4B_OK : Q4B_ERR_ARG;
+}
 
 // argument checks shared by q4b_gemm_addend and q4b_gemm_wt_addend
 static int check_gemm_args(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,

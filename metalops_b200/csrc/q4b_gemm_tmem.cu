@@ -22,7 +22,6 @@
 // Every mbarrier wait is bounded; a wait that gives up records a code and all roles fall through
 // to the common exit.
 #include <mutex>
-#include <mutex>
 
 #include "q4b_sm100_ptx.cuh"
 
@@ -56,16 +55,6 @@ static_assert(NSTAGE * STAGE_BYTES + SX * X_STAGE_BYTES >= MAX_ROWS * PANEL_N * 
 static_assert(SMEM_X % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 
 __device__ int g_status = 0;
-
-template <bool BF16> __device__ __forceinline__ uint32_t scale_pair(uint16_t dbits) {
-    if constexpr (BF16) {
-        __nv_bfloat16 b = __float2bfloat16_rn(__half2float(__ushort_as_half(dbits)));
-        uint32_t u = __bfloat16_as_ushort(b);
-        return u | (u << 16);
-    } else {
-        return (uint32_t)dbits | ((uint32_t)dbits << 16);
-    }
-}
 
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -178,29 +167,8 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
             if (!mbar_wait_warp(bar_full_w(slot), (q / NSTAGE) & 1, abort_flag, &g_status, 405)) goto done;
             if (!mbar_wait_warp(bar_a_empty(st), ((i / TM_STAGES) & 1) ^ 1, abort_flag, &g_status, 406)) goto done;
             tc_fence_after();
-            const uint32_t wst = base + SMEM_RING + slot * STAGE_BYTES + (i % STAGE_STEPS) * TILE_BYTES;
-            uint32_t w[2][4];
-#pragma unroll
-            for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kb][c]) : "r"(wst + woff[c] + kb * 8));
-            uint32_t dbits[2];
-            asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits[0]) : "r"(wst + doff));
-            asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits[1]) : "r"(wst + doff + 4));
-#pragma unroll
-            for (int kb = 0; kb < 2; ++kb) {
-                const uint32_t d2 = scale_pair<BF16>((uint16_t)dbits[kb]);
-                uint32_t regs[16];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t h[4];
-                    dequant_word<BF16>(w[kb][c], h);
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) regs[4 * c + s] = BF16 ? bmul2_bits(h[s], d2) : hmul2_bits(h[s], d2);
-                }
-                tc_st_32x32b_x16(lane_taddr + (uint32_t)(A_COL0 + st * 32 + kb * 16), regs);
-            }
+            dequant_tile_to_tmem<BF16>(base + SMEM_RING + slot * STAGE_BYTES + (i % STAGE_STEPS) * TILE_BYTES, woff, doff,
+                                       lane_taddr + (uint32_t)(A_COL0 + st * 32));
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -277,25 +245,6 @@ done:
     }
 }
 
-// cuTensorMapEncodeTiled through the runtime, so the library has no link dependency on libcuda
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-        else
-            (void)cudaGetLastError();
-    });
-    return fn;
-}
-
 // k-split: the number of CTAs per panel that needs the fewest (waves of CTAs) x (k-tiles per CTA)
 static int choose_ksplit(int64_t panels, int64_t KU, int sms) {
     int best = 1;
@@ -358,18 +307,9 @@ int device_sm_count();
 int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
                      const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st) {
     if (M < 1 || M > gemmtm::MAX_ROWS) return Q4B_ERR_SHAPE;
-    gemmtm::EncodeTiledFn enc = gemmtm::get_encode_fn();
-    if (enc == nullptr) return Q4B_ERR_CUDA;
     const int rows = (M + 15) / 16 * 16;                                   // the MMA's N: a multiple of 16
     CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)rows};      // 64 k x `rows` rows per copy
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&tmap, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x),
-                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return Q4B_ERR_ARG;
+    if (int rc = encode_x_tensor_map(&tmap, x, bf16, M, K, ldx, rows)) return rc;       // 64 k x `rows` rows per copy
     const int sms = device_sm_count();
     const int act = act_of_flags(flags);
     return bf16 ? gemmtm::launch<true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, flags, sms, st)

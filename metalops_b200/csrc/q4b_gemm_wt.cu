@@ -59,16 +59,6 @@ static_assert(SMEM_DYN <= 227 * 1024, "shared memory");
 
 __device__ int g_status = 0;
 
-template <bool BF16> __device__ __forceinline__ uint32_t scale_pair(uint16_t dbits) {
-    if constexpr (BF16) {
-        __nv_bfloat16 b = __float2bfloat16_rn(__half2float(__ushort_as_half(dbits)));
-        uint32_t u = __bfloat16_as_ushort(b);
-        return u | (u << 16);
-    } else {
-        return (uint32_t)dbits | ((uint32_t)dbits << 16);
-    }
-}
-
 // GENERAL: the epilogue adds the fp32 addend and applies the activation; without it (its own instantiation,
 // so that the common case keeps its registers) it only converts and stores.
 template <bool BF16, bool GENERAL>
@@ -289,29 +279,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                 if (!mbar_wait_warp(bar_full_w(wslot, fill), (fill >> 1) & 1, abort_flag, &g_status, 607)) goto done;
                 if (!mbar_wait_warp(bar_empty(s), ((gq / ST) & 1) ^ 1, abort_flag, &g_status, 608)) goto done;
                 tc_fence_after();
-                const uint32_t wst = base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES;
-                uint32_t w[2][4];
-#pragma unroll
-                for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kb][c]) : "r"(wst + woff[c] + kb * 8));
-                uint32_t dbits[2];
-                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits[0]) : "r"(wst + doff));
-                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits[1]) : "r"(wst + doff + 4));
-#pragma unroll
-                for (int kb = 0; kb < 2; ++kb) {
-                    const uint32_t d2 = scale_pair<BF16>((uint16_t)dbits[kb]);
-                    uint32_t regs[16];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t h[4];
-                        dequant_word<BF16>(w[kb][c], h);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) regs[4 * c + e] = BF16 ? bmul2_bits(h[e], d2) : hmul2_bits(h[e], d2);
-                    }
-                    tc_st_32x32b_x16(lane_taddr + (uint32_t)(A_COL0 + (s * STAGE_STEPS + sub) * 32 + kb * 16), regs);
-                }
+                dequant_tile_to_tmem<BF16>(base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES, woff, doff,
+                                           lane_taddr + (uint32_t)(A_COL0 + (s * STAGE_STEPS + sub) * 32));
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -344,25 +313,6 @@ done:
     }
 }
 
-// cuTensorMapEncodeTiled through the runtime, so the library has no link dependency on libcuda
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-        else
-            (void)cudaGetLastError();
-    });
-    return fn;
-}
-
 template <bool BF16, bool GENERAL>
 static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t K, int64_t N, void *y, int64_t ldy,
                   const float *addend, int64_t ld_add, int rows, int act, int sms, cudaStream_t st) {
@@ -393,24 +343,11 @@ int device_sm_count();
 int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, const float *addend,
                    int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st) {
     if (M < 1) return Q4B_ERR_SHAPE;
-    gemmwt::EncodeTiledFn enc = gemmwt::get_encode_fn();
-    if (enc == nullptr) return Q4B_ERR_CUDA;
-    // Height of a row tile (the MMAs' N, a multiple of 16, at most 256): equal heights rather than full
-    // tiles and a remainder (M = 300: two tiles of 160 rows, not 256 + 44).  Lower tiles than the rows
-    // need never pay: an MMA of 128 rows takes the tensor pipe 97 cycles against 128 for one of 256
-    // (measured), so even a tile count that fills the last wave of items better loses.
     const int sms = device_sm_count();
     const int t = (M + gemmwt::MAX_ROWS - 1) / gemmwt::MAX_ROWS;
     const int rows = ((M + t - 1) / t + 15) / 16 * 16;
     CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)rows};                   // 64 k x `rows` rows per copy
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&tmap, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x),
-                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return Q4B_ERR_ARG;
+    if (int rc = encode_x_tensor_map(&tmap, x, bf16, M, K, ldx, rows)) return rc;       // 64 k x `rows` rows per copy
     const int act = act_of_flags(flags);
     if (addend != nullptr || act != 0)
         return bf16 ? gemmwt::launch<true, true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st)

@@ -131,5 +131,40 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, int m, int n) {
            | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// One k-tile of a 128-column panel, packed in shared memory at `wst` (eight 576-byte tiles, `run` bytes
+// apart), dequantised into 32 columns of tensor memory at `taddr` as the tcgen05 A operand: a warp covers
+// one lane quadrant, thread = output column, (q - 8) * d rounded once to the activations' type.
+// woff[c] / doff: the thread's byte offsets of nibble word c and of its scale inside the k-tile.
+template <bool BF16>
+__device__ __forceinline__ void dequant_tile_to_tmem(uint32_t wst, const uint32_t (&woff)[4], uint32_t doff, uint32_t taddr) {
+    uint32_t w[2][4];
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kb][c]) : "r"(wst + woff[c] + kb * 8));
+    uint32_t dbits[2];
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits[0]) : "r"(wst + doff));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits[1]) : "r"(wst + doff + 4));
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+        const uint32_t d2 = scale_pair<BF16>((uint16_t)dbits[kb]);
+        uint32_t regs[16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t h[4];
+            dequant_word<BF16>(w[kb][c], h);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) regs[4 * c + e] = BF16 ? bmul2_bits(h[e], d2) : hmul2_bits(h[e], d2);
+        }
+        tc_st_32x32b_x16(taddr + (uint32_t)(kb * 16), regs);
+    }
+}
+
 }  // namespace ptx
+
+// Tensor map of the activations X [M, K] (K contiguous, leading dimension ldx) for copies of
+// 64 k x `rows` rows with the 128-byte swizzle; rows beyond M read as zero.  Defined in q4b_gemm.cu.
+int encode_x_tensor_map(CUtensorMap *map, const void *x, int bf16, int64_t M, int64_t K, int64_t ldx, int rows);
+
 }  // namespace q4b
