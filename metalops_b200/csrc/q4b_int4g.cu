@@ -145,8 +145,8 @@ int4g_corr_kernel(const TS *__restrict__ scales, const TS *__restrict__ zeros, i
 //                        X is read once.
 //   int4g_addend_kernel  a CTA takes 512 columns x 32 rows: a thread owns two columns, their corr[g, n]
 //                        values arrive 16 groups at a time (coalesced over the CTA), the rows' group sums
-//                        are broadcast from shared memory (one 16-byte read feeds eight FMAs), 2 x 32
-//                        accumulators per thread, coalesced fp32 stores.  corr is re-read once per row
+//                        are broadcast from shared memory (one 16-byte read of four rows feeds four
+//                        two-wide FMAs, fma.rn.f32x2), 2 x 32 accumulators per thread, coalesced fp32 stores.  corr is re-read once per row
 //                        tile, from L2.
 template <typename TX>
 __global__ void __launch_bounds__(256)
@@ -154,8 +154,15 @@ int4g_rowsum_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t K,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t pairs = M * G;
     for (int64_t p = (int64_t)blockIdx.x * 8 + warp; p < pairs; p += (int64_t)gridDim.x * 8) {
-        const int64_t m = p / G;
-        const int g = (int)(p % G);
+        int64_t m;
+        int g;
+        if (pairs < (1LL << 31)) {                       // the usual case: 32-bit division
+            m = (int)((unsigned)p / (unsigned)G);
+            g = (int)((unsigned)p % (unsigned)G);
+        } else {
+            m = p / G;
+            g = (int)(p % G);
+        }
         const TX *xr = x + m * ldx;
         const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
         float s = 0.0f;
@@ -170,59 +177,74 @@ constexpr int ADD_ROWS = 32;       // rows per CTA of the addend kernel: corr is
 constexpr int ADD_COLS = 512;      // columns per CTA: two per thread, so a broadcast read of four group sums feeds eight FMAs
 constexpr int ADD_GCHUNK = 16;     // groups per pass
 
+// two independent fp32 FMAs in one instruction: d = a * b + c on both halves of the pairs
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long &>(d))
+        : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)),
+          "l"(reinterpret_cast<const unsigned long long &>(c)));
+    return d;
+}
+
 __global__ void __launch_bounds__(256, 2)
 int4g_addend_kernel(const float *__restrict__ rowsums, int64_t M, const float *__restrict__ corr,
                     const float *__restrict__ bias, int64_t N, int G, float *__restrict__ addend) {
-    __shared__ __align__(16) float rs[ADD_ROWS][ADD_GCHUNK];
+    __shared__ __align__(16) float rs[ADD_GCHUNK][ADD_ROWS];                    // [group][row]: four rows per 16-byte read
     const int64_t n = (int64_t)blockIdx.x * ADD_COLS + 2 * threadIdx.x;          // this thread's columns: n, n + 1
     const int64_t m0 = (int64_t)blockIdx.y * ADD_ROWS;
     const int nrows = (int)min((int64_t)ADD_ROWS, M - m0);
     const bool ok0 = n < N, ok1 = n + 1 < N;
     const bool pair = ok1 && (N % 2 == 0);                                        // both columns, 8-byte aligned
-    float acc0[ADD_ROWS], acc1[ADD_ROWS];
+    float2 acc0[ADD_ROWS / 2], acc1[ADD_ROWS / 2];                                // (row 2i, row 2i + 1) of column n / n + 1
     const float b0 = (bias != nullptr && ok0) ? bias[n] : 0.0f, b1 = (bias != nullptr && ok1) ? bias[n + 1] : 0.0f;
 #pragma unroll
-    for (int r = 0; r < ADD_ROWS; ++r) { acc0[r] = b0; acc1[r] = b1; }
+    for (int r = 0; r < ADD_ROWS / 2; ++r) { acc0[r] = make_float2(b0, b0); acc1[r] = make_float2(b1, b1); }
     for (int g0 = 0; g0 < G; g0 += ADD_GCHUNK) {
         __syncthreads();
         for (int i = threadIdx.x; i < ADD_ROWS * ADD_GCHUNK; i += 256) {
-            const int r = i / ADD_GCHUNK, g = g0 + i % ADD_GCHUNK;
-            rs[r][i % ADD_GCHUNK] = (r < nrows && g < G) ? rowsums[(m0 + r) * G + g] : 0.0f;
+            const int r = i / ADD_GCHUNK, j = i % ADD_GCHUNK;                    // consecutive threads: consecutive groups of a row
+            rs[j][r] = (r < nrows && g0 + j < G) ? rowsums[(m0 + r) * G + g0 + j] : 0.0f;
         }
-        float c0[ADD_GCHUNK], c1[ADD_GCHUNK];
+        float2 c0[ADD_GCHUNK], c1[ADD_GCHUNK];                                    // corr[g, n] and corr[g, n + 1], each twice
 #pragma unroll
         for (int j = 0; j < ADD_GCHUNK; ++j) {
             const float *cp = corr + (int64_t)(g0 + j) * N + n;
+            float v0, v1;
             if (g0 + j < G && pair) {
                 const float2 v = *reinterpret_cast<const float2 *>(cp);
-                c0[j] = v.x;
-                c1[j] = v.y;
+                v0 = v.x;
+                v1 = v.y;
             } else {
-                c0[j] = (g0 + j < G && ok0) ? cp[0] : 0.0f;
-                c1[j] = (g0 + j < G && ok1) ? cp[1] : 0.0f;
+                v0 = (g0 + j < G && ok0) ? cp[0] : 0.0f;
+                v1 = (g0 + j < G && ok1) ? cp[1] : 0.0f;
             }
+            c0[j] = make_float2(v0, v0);
+            c1[j] = make_float2(v1, v1);
         }
         __syncthreads();
 #pragma unroll
-        for (int r = 0; r < ADD_ROWS; ++r) {
+        for (int j = 0; j < ADD_GCHUNK; ++j) {
 #pragma unroll
-            for (int j = 0; j < ADD_GCHUNK; j += 4) {
-                const float4 v = *reinterpret_cast<const float4 *>(&rs[r][j]);      // the same address in every lane: a broadcast
-                acc0[r] = fmaf(c0[j], v.x, acc0[r]);      acc1[r] = fmaf(c1[j], v.x, acc1[r]);
-                acc0[r] = fmaf(c0[j + 1], v.y, acc0[r]);  acc1[r] = fmaf(c1[j + 1], v.y, acc1[r]);
-                acc0[r] = fmaf(c0[j + 2], v.z, acc0[r]);  acc1[r] = fmaf(c1[j + 2], v.z, acc1[r]);
-                acc0[r] = fmaf(c0[j + 3], v.w, acc0[r]);  acc1[r] = fmaf(c1[j + 3], v.w, acc1[r]);
+            for (int r = 0; r < ADD_ROWS; r += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(&rs[j][r]);    // the same address in every lane: a broadcast
+                const float2 lo = make_float2(v.x, v.y), hi = make_float2(v.z, v.w);
+                acc0[r / 2] = fma2(c0[j], lo, acc0[r / 2]);
+                acc0[r / 2 + 1] = fma2(c0[j], hi, acc0[r / 2 + 1]);
+                acc1[r / 2] = fma2(c1[j], lo, acc1[r / 2]);
+                acc1[r / 2 + 1] = fma2(c1[j], hi, acc1[r / 2 + 1]);
             }
         }
     }
 #pragma unroll
     for (int r = 0; r < ADD_ROWS; ++r) {
         if (r < nrows) {
+            const float a0 = (r & 1) ? acc0[r / 2].y : acc0[r / 2].x, a1 = (r & 1) ? acc1[r / 2].y : acc1[r / 2].x;
             float *op = addend + (m0 + r) * N + n;
-            if (pair) *reinterpret_cast<float2 *>(op) = make_float2(acc0[r], acc1[r]);
+            if (pair) *reinterpret_cast<float2 *>(op) = make_float2(a0, a1);
             else {
-                if (ok0) op[0] = acc0[r];
-                if (ok1) op[1] = acc1[r];
+                if (ok0) op[0] = a0;
+                if (ok1) op[1] = a1;
             }
         }
     }
