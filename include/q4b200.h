@@ -197,6 +197,23 @@ Q4B_API size_t q4b_int4g_rowsums_bytes(int64_t M, int64_t K, int64_t group);
 Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr,
                              const float *bias, int64_t K, int64_t N, int64_t group, float *rowsums_ws,
                              float *addend_out, void *stream);
+/*
+ * The zero-point term folded into the contraction, for the persistent prefill kernel: instead of an
+ * [M, N] fp32 addend, KX = q4b_int4g_fold_ktiles(K, group) further k-tiles multiply
+ *   fold_rows    [M, 64 KX] bf16, from X per call (q4b_int4g_fold_rows: the rows' group sums), by
+ *   fold_operand [N, 64 KX] bf16, from corr once per weight (q4b_int4g_fold_operand).
+ * Both factors are split into three bf16 terms and the six largest products kept, so the term keeps
+ * fp32-like accuracy (what is dropped is below 2^-24 of it).  q4b_int4g_gemm_fold runs the product;
+ * bias is one fp32 row of N values or NULL.
+ */
+Q4B_API int q4b_int4g_fold_ktiles(int64_t K, int64_t group);
+Q4B_API int q4b_int4g_fold_operand(const float *corr, int64_t K, int64_t N, int64_t group, void *operand_out,
+                                   void *stream);
+Q4B_API int q4b_int4g_fold_rows(const void *x, int x_dtype, int64_t M, int64_t ldx, int64_t K, int64_t group,
+                                void *rows_out, void *stream);
+Q4B_API int q4b_int4g_gemm_fold(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+                                int64_t K, int64_t N, const void *fold_operand, const void *fold_rows, int KX,
+                                const float *bias, void *y, int64_t ldy, int flags, void *stream);
 Q4B_API int q4b_int4g_matmul_generic(const void *x, int x_dtype, int64_t M, int64_t ldx,
                                      const void *packed, const void *scales, const void *zeros,
                                      int sz_dtype, int64_t K, int64_t N, int64_t group, void *y,

@@ -19,7 +19,8 @@ int device_sm_count();
 int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
                      const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
 int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, const float *addend,
-                   int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
+                   int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st, const void *corr_op = nullptr,
+                   const void *xr = nullptr, int KX = 0);
 int gemv_wait_status(int *value);
 int gemm_tmem_wait_status(int *value);
 int gemm_wt_wait_status(int *value);
@@ -98,6 +99,19 @@ extern "C" int q4b_gemm_wt_addend(const void *x, int x_dtype, int64_t M, int64_t
                                   void *stream) {
     if (int rc = check_gemm_args(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags)) return rc;
     return gemm_wt_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, (cudaStream_t)stream);
+}
+
+// The group-wise INT4 product with its zero-point term folded into the contraction (persistent prefill
+// kernel, any M >= 1): KX further k-tiles multiply fold_rows [M, 64 KX] by fold_operand [N, 64 KX] (both
+// bf16, from q4b_int4g_fold_rows / q4b_int4g_fold_operand).  bias: one fp32 row of N values, or NULL.
+extern "C" int q4b_int4g_gemm_fold(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                                   const void *fold_operand, const void *fold_rows, int KX, const float *bias, void *y,
+                                   int64_t ldy, int flags, void *stream) {
+    if (int rc = check_gemm_args(x, x_dtype, M, ldx, prepacked, K, N, bias, 0, y, ldy, flags)) return rc;
+    if (fold_operand == nullptr || fold_rows == nullptr || KX < 1 || KX > 4096) return Q4B_ERR_ARG;
+    if (!aligned(fold_operand, 16) || !aligned(fold_rows, 16)) return Q4B_ERR_ALIGN;
+    return gemm_wt_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, bias, 0, y, ldy, flags, (cudaStream_t)stream,
+                          fold_operand, fold_rows, KX);
 }
 
 // Synchronises the stream, then reads and clears the status words of every kernel with bounded waits.

@@ -63,7 +63,8 @@ __device__ int g_status = 0;
 // so that the common case keeps its registers) it only converts and stores.
 template <bool BF16, bool GENERAL>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked, int M, int64_t K, int64_t N,
+gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_r,
+               const uint8_t *__restrict__ prepacked, const uint16_t *__restrict__ corr_op, int KX, int M, int64_t K, int64_t N,
                uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add, int rows, int act) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t s_tmem_base;
@@ -87,7 +88,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
     const int panels = (NT + PANEL_TILES - 1) / PANEL_TILES;
     const int row_tiles = (M + rows - 1) / rows;               // `rows`: height of a row tile, chosen by the host
     const int items = panels * row_tiles;
-    const int spi = (KU + STAGE_STEPS - 1) / STAGE_STEPS;                  // stages per item
+    // Folded rank-G term (GENERAL only): KX further k-tiles whose A operand is read as bf16 from corr_op
+    // [N, 64 KX] and whose X slices come from a second tensor map (bf16 [M, 64 KX]); KT counts all k-tiles.
+    const int KT = KU + (GENERAL ? KX : 0);
+    const int spi = (KT + STAGE_STEPS - 1) / STAGE_STEPS;                  // stages per item
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -122,7 +126,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
             for (int q = 0; q < spi; ++q, ++gq) {
                 const int slot = gq % NSTAGE_W, fill = gq / NSTAGE_W;
                 if (!mbar_wait_warp(bar_empty_w(slot), (fill & 1) ^ 1, abort_flag, &g_status, 601)) goto done;
-                const uint32_t bytes = (uint32_t)(min(STAGE_STEPS, KU - q * STAGE_STEPS) * TILE_BYTES);
+                const int nreg = max(0, min(STAGE_STEPS, KU - q * STAGE_STEPS));        // packed k-tiles of the stage
+                const uint32_t bytes = (uint32_t)(nreg * TILE_BYTES);
+                if (nreg == 0) {                          // a stage of the folded term only: nothing to copy
+                    if (lane == 0) mbar_arrive(bar_full_w(slot, fill));
+                    continue;
+                }
                 if (lane == 0) mbar_arrive_expect_tx(bar_full_w(slot, fill), (uint32_t)valid * bytes);
                 __syncwarp();
                 if (lane < valid)
@@ -139,11 +148,14 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                 for (int q = 0; q < spi; ++q, ++gq) {
                     const int s = gq % ST;
                     if (!mbar_wait(bar_empty(s), ((gq / ST) & 1) ^ 1, abort_flag, &g_status, 602)) goto done;
-                    const int nk = min(STAGE_STEPS, KU - q * STAGE_STEPS);
+                    const int nk = min(STAGE_STEPS, KT - q * STAGE_STEPS);
                     mbar_arrive_expect_tx(bar_full(s), (uint32_t)(nk * rows * TILE_K * 2));
-                    for (int j = 0; j < nk; ++j)
-                        tma_load_2d(base + SMEM_X + s * X_STAGE_BYTES + j * X_TILE_BYTES, &tmap_x, (q * STAGE_STEPS + j) * TILE_K, row0,
-                                    bar_full(s));
+                    for (int j = 0; j < nk; ++j) {
+                        const int tile = q * STAGE_STEPS + j;
+                        const uint32_t dst = base + SMEM_X + s * X_STAGE_BYTES + j * X_TILE_BYTES;
+                        if (tile < KU) tma_load_2d(dst, &tmap_x, tile * TILE_K, row0, bar_full(s));
+                        else tma_load_2d(dst, &tmap_r, (tile - KU) * TILE_K, row0, bar_full(s));
+                    }
                 }
             }
         }
@@ -153,7 +165,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
         // pair, and the tensor pipe queues only an instruction or two: hence one wait and one commit per
         // stage of eight MMAs.  (Splitting the rows between two issuing warps is slower: an MMA of 128
         // rows takes the pipe about 97 cycles, not half of the 128 that one of 256 rows takes.)
-        const uint32_t idesc = make_idesc(BF16, PANEL_N, rows);
+        const uint32_t idesc = make_idesc(BF16, PANEL_N, rows), idesc_fold = make_idesc(true, PANEL_N, rows);   // the folded term is bf16
         int gq = 0, itl = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++itl) {
             if (!mbar_wait_warp(bar_d_empty, (uint32_t)(itl & 1) ^ 1u, abort_flag, &g_status, 603)) goto done;   // the previous item was read out
@@ -165,13 +177,15 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                 if (elect_one()) {
                     const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_X + s * X_STAGE_BYTES);
                     const uint32_t a0 = tmem_base + (uint32_t)(A_COL0 + s * STAGE_STEPS * 32);
+                    const uint32_t id0 = q * STAGE_STEPS < KU ? idesc : idesc_fold;
+                    const uint32_t id1 = q * STAGE_STEPS + 1 < KU ? idesc : idesc_fold;
 #pragma unroll
                     for (int k = 0; k < TILE_K / 16; ++k)
-                        tc_mma_ts_f16(tmem_base + D_COL0, a0 + k * 8, bdesc + 2 * k, idesc, (uint32_t)((q | k) != 0));
-                    if (q * STAGE_STEPS + 1 < KU) {
+                        tc_mma_ts_f16(tmem_base + D_COL0, a0 + k * 8, bdesc + 2 * k, id0, (uint32_t)((q | k) != 0));
+                    if (q * STAGE_STEPS + 1 < KT) {
 #pragma unroll
                         for (int k = 0; k < TILE_K / 16; ++k)
-                            tc_mma_ts_f16(tmem_base + D_COL0, a0 + 32 + k * 8, bdesc + (X_TILE_BYTES >> 4) + 2 * k, idesc, 1u);
+                            tc_mma_ts_f16(tmem_base + D_COL0, a0 + 32 + k * 8, bdesc + (X_TILE_BYTES >> 4) + 2 * k, id1, 1u);
                     }
                     tc_commit(bar_empty(s));
                     if (q == spi - 1) tc_commit(bar_d_full);
@@ -229,18 +243,35 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                             }
                         } else {
                             // the addend's sixteen values first, all loads in flight together: interleaved
-                            // with the stores they would wait for one another (the stores may alias them)
+                            // with the stores they would wait for one another (the stores may alias them);
+                            // a bias row (ld_add = 0) is one value for the whole column
                             const int jn = min(16, M - m0);
                             float a[16];
+                            if (addend == nullptr || ld_add == 0) {
+                                const float b = addend != nullptr ? __ldg(addend + n) : 0.0f;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                a[j] = (addend != nullptr && j < jn) ? __ldg(addend + (size_t)(m0 + j) * ld_add + n) : 0.0f;
+                                for (int j = 0; j < 16; ++j) a[j] = b;
+                            } else {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j, yp += ldy) {
-                                if (j < jn) {
-                                    const float f = apply_act(__uint_as_float(v[u][j]) + a[j], act);    // fp32 term added before the one rounding
-                                    if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-                                    else *yp = __half_as_ushort(__float2half_rn(f));
+                                for (int j = 0; j < 16; ++j) a[j] = j < jn ? __ldg(addend + (size_t)(m0 + j) * ld_add + n) : 0.0f;
+                            }
+                            if (act == 0) {                       // uniform: the activation switch once per chunk
+#pragma unroll
+                                for (int j = 0; j < 16; ++j, yp += ldy) {
+                                    if (j < jn) {
+                                        const float f = __uint_as_float(v[u][j]) + a[j];          // fp32 term added before the one rounding
+                                        if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                                        else *yp = __half_as_ushort(__float2half_rn(f));
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j, yp += ldy) {
+                                    if (j < jn) {
+                                        const float f = apply_act(__uint_as_float(v[u][j]) + a[j], act);
+                                        if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                                        else *yp = __half_as_ushort(__float2half_rn(f));
+                                    }
                                 }
                             }
                         }
@@ -270,17 +301,33 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
         // before its own being outstanding; that fill was consumed before the producer issued the one in
         // between, which it issued before the fill this group has already seen land (two stages back).
         int gbase = 0, itl = 0;                                   // global index of the item's first k-tile
-        for (int item = blockIdx.x; item < items; item += gridDim.x, ++itl, gbase += KU) {
+        for (int item = blockIdx.x; item < items; item += gridDim.x, ++itl, gbase += KT) {
             // this group's k-tiles of the item: those whose global index is grp modulo the number of groups
             int i = (grp - gbase % DEQ_GROUPS + DEQ_GROUPS) % DEQ_GROUPS;
-            for (; i < KU; i += DEQ_GROUPS) {
+            for (; i < KT; i += DEQ_GROUPS) {
                 const int gq = itl * spi + i / STAGE_STEPS, sub = i % STAGE_STEPS;
                 const int wslot = gq % NSTAGE_W, fill = gq / NSTAGE_W, s = gq % ST;
                 if (!mbar_wait_warp(bar_full_w(wslot, fill), (fill >> 1) & 1, abort_flag, &g_status, 607)) goto done;
                 if (!mbar_wait_warp(bar_empty(s), ((gq / ST) & 1) ^ 1, abort_flag, &g_status, 608)) goto done;
                 tc_fence_after();
-                dequant_tile_to_tmem<BF16>(base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES, woff, doff,
-                                           lane_taddr + (uint32_t)(A_COL0 + (s * STAGE_STEPS + sub) * 32));
+                const uint32_t a_addr = lane_taddr + (uint32_t)(A_COL0 + (s * STAGE_STEPS + sub) * 32);
+                if (!GENERAL || i < KU) {
+                    dequant_tile_to_tmem<BF16>(base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES, woff, doff, a_addr);
+                } else {
+                    // a k-tile of the folded term: this thread's column of corr_op, 64 bf16 = 2 x 16 words
+                    const int64_t n = (int64_t)(item % panels) * PANEL_N + wq * 32 + lane;
+                    const uint4 *src = reinterpret_cast<const uint4 *>(corr_op + (size_t)n * (size_t)(KX * TILE_K) + (size_t)(i - KU) * TILE_K);
+#pragma unroll
+                    for (int kb = 0; kb < 2; ++kb) {
+                        uint32_t regs[16];
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            const uint4 t = n < N ? __ldg(src + kb * 4 + v4) : make_uint4(0u, 0u, 0u, 0u);
+                            regs[4 * v4] = t.x; regs[4 * v4 + 1] = t.y; regs[4 * v4 + 2] = t.z; regs[4 * v4 + 3] = t.w;
+                        }
+                        tc_st_32x32b_x16(a_addr + (uint32_t)(kb * 16), regs);
+                    }
+                }
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -289,7 +336,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__rest
                     mbar_arrive(bar_empty_w(wslot));
                     // a stage that holds a single k-tile (odd number of k-tiles, the item's last stage) still
                     // has to collect the arrivals of two
-                    if ((KU & 1) && i == KU - 1) {
+                    if ((KT & 1) && i == KT - 1) {
                         mbar_arrive(bar_full(s));
                         mbar_arrive(bar_empty_w(wslot));
                     }
@@ -314,8 +361,9 @@ done:
 }
 
 template <bool BF16, bool GENERAL>
-static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t K, int64_t N, void *y, int64_t ldy,
-                  const float *addend, int64_t ld_add, int rows, int act, int sms, cudaStream_t st) {
+static int launch(const CUtensorMap &tmap, const CUtensorMap &tmap_r, const void *prepacked, const void *corr_op, int KX, int M,
+                  int64_t K, int64_t N, void *y, int64_t ldy, const float *addend, int64_t ld_add, int rows, int act, int sms,
+                  cudaStream_t st) {
     {   // opt in to the large dynamic shared memory once per device and instantiation
         static bool attr_done[64] = {};
         static std::mutex attr_mu;
@@ -329,8 +377,8 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t
     }
     const int64_t items = ceil_div(tiles_n(N), PANEL_TILES) * ceil_div(M, rows);
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    gemm_wt_kernel<BF16, GENERAL><<<grid, THREADS, SMEM_DYN, st>>>(tmap, (const uint8_t *)prepacked, M, K, N, (uint16_t *)y, ldy, addend,
-                                                        ld_add, rows, act);
+    gemm_wt_kernel<BF16, GENERAL><<<grid, THREADS, SMEM_DYN, st>>>(tmap, tmap_r, (const uint8_t *)prepacked, (const uint16_t *)corr_op, KX,
+                                                                  M, K, N, (uint16_t *)y, ldy, addend, ld_add, rows, act);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }
@@ -339,21 +387,32 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t
 
 int device_sm_count();
 
-// Arguments as checked by the matmul entry points; M >= 1.
+// Arguments as checked by the matmul entry points; M >= 1.  corr_op / xr / KX: the folded rank-G term of the
+// group-wise format (KX k-tiles; bf16 [N, 64 KX] and [M, 64 KX]), or null / 0.
 int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, const float *addend,
-                   int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st) {
+                   int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st, const void *corr_op, const void *xr, int KX) {
     if (M < 1) return Q4B_ERR_SHAPE;
+    // Height of a row tile (the MMAs' N, a multiple of 16, at most 256): equal heights rather than full
+    // tiles and a remainder (M = 300: two tiles of 160 rows, not 256 + 44).  Lower tiles than the rows
+    // need never pay: an MMA of 128 rows takes the tensor pipe 97 cycles against 128 for one of 256
+    // (measured), so even a tile count that fills the last wave of items better loses.
     const int sms = device_sm_count();
     const int t = (M + gemmwt::MAX_ROWS - 1) / gemmwt::MAX_ROWS;
     const int rows = ((M + t - 1) / t + 15) / 16 * 16;
-    CUtensorMap tmap;
+    CUtensorMap tmap, tmap_r;
     if (int rc = encode_x_tensor_map(&tmap, x, bf16, M, K, ldx, rows)) return rc;       // 64 k x `rows` rows per copy
+    const bool fold = corr_op != nullptr && xr != nullptr && KX > 0;
+    if (fold) {
+        if (int rc = encode_x_tensor_map(&tmap_r, xr, 1, M, (int64_t)KX * TILE_K, (int64_t)KX * TILE_K, rows)) return rc;
+    } else {
+        tmap_r = tmap;
+    }
     const int act = act_of_flags(flags);
-    if (addend != nullptr || act != 0)
-        return bf16 ? gemmwt::launch<true, true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st)
-                    : gemmwt::launch<false, true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st);
-    return bf16 ? gemmwt::launch<true, false>(tmap, prepacked, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st)
-                : gemmwt::launch<false, false>(tmap, prepacked, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st);
+    if (addend != nullptr || act != 0 || fold)
+        return bf16 ? gemmwt::launch<true, true>(tmap, tmap_r, prepacked, corr_op, fold ? KX : 0, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st)
+                    : gemmwt::launch<false, true>(tmap, tmap_r, prepacked, corr_op, fold ? KX : 0, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st);
+    return bf16 ? gemmwt::launch<true, false>(tmap, tmap_r, prepacked, nullptr, 0, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st)
+                : gemmwt::launch<false, false>(tmap, tmap_r, prepacked, nullptr, 0, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st);
 }
 
 // read and clear this file's wait status (host side; the caller has synchronised the stream)

@@ -250,6 +250,77 @@ int4g_addend_kernel(const float *__restrict__ rowsums, int64_t M, const float *_
     }
 }
 
+// ---- the zero-point term folded into the tensor-core contraction --------------------------------------
+// sum_g R[m, g] * C[g, n] needs fp32-like accuracy from bf16 operands: each factor is split into three bf16
+// terms (hi + mid + lo = 24 bits) and the six largest products are kept (hi.hi, mid.hi, hi.mid, lo.hi,
+// hi.lo, mid.mid; what is dropped is below 2^-24 of |R C|).  That makes 6 G extra k, padded with zeros to
+// whole 64-k tiles.  Segment s of the extra k range holds, for g = 0..G-1:
+//      rows  (X side):    R_hi, R_mid, R_hi,  R_lo, R_hi, R_mid
+//      operand (W side):  C_hi, C_hi,  C_mid, C_hi, C_lo, C_mid
+__device__ __forceinline__ void split3_bf16(float v, uint16_t &hi, uint16_t &mid, uint16_t &lo) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h);                   // exact
+    const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(m);                  // exact
+    hi = __bfloat16_as_ushort(h);
+    mid = __bfloat16_as_ushort(m);
+    lo = __bfloat16_as_ushort(__float2bfloat16_rn(r2));
+}
+
+// out [N, E] bf16 from corr [G, N] fp32; E = 64 * ceil(6 G / 64).  A thread per (n, g).
+__global__ void __launch_bounds__(256)
+int4g_fold_operand_kernel(const float *__restrict__ corr, int G, int64_t N, int E, uint16_t *__restrict__ out) {
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t n = idx % N;                                   // consecutive threads: consecutive columns of corr
+    const int64_t g = idx / N;
+    if (g >= G) {
+        // the threads past the last group clear the padding of their column
+        const int64_t pad = g - G;
+        if (pad == 0)
+            for (int e = 6 * G; e < E; ++e) out[n * E + e] = 0;
+        return;
+    }
+    uint16_t hi, mid, lo;
+    split3_bf16(corr[g * N + n], hi, mid, lo);
+    uint16_t *o = out + n * E + g;
+    o[0] = hi; o[G] = hi; o[2 * G] = mid; o[3 * G] = hi; o[4 * G] = lo; o[5 * G] = mid;
+}
+
+// rows [M, E] bf16 from X: a warp per (row, group) as in int4g_rowsum_kernel, same summation order.
+template <typename TX>
+__global__ void __launch_bounds__(256)
+int4g_fold_rows_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t K, int64_t group, int G, int E,
+                       uint16_t *__restrict__ rows_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gpad = (E - 6 * G + 0);                            // zeros to write per row, by the row's first warp
+    const int64_t pairs = M * G;
+    for (int64_t p = (int64_t)blockIdx.x * 8 + warp; p < pairs; p += (int64_t)gridDim.x * 8) {
+        int64_t m;
+        int g;
+        if (pairs < (1LL << 31)) {
+            m = (int)((unsigned)p / (unsigned)G);
+            g = (int)((unsigned)p % (unsigned)G);
+        } else {
+            m = p / G;
+            g = (int)(p % G);
+        }
+        const TX *xr = x + m * ldx;
+        const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
+        float s = 0.0f;
+        for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        uint16_t *o = rows_out + m * E;
+        if (lane == 0) {
+            uint16_t hi, mid, lo;
+            split3_bf16(s, hi, mid, lo);
+            o[g] = hi; o[G + g] = mid; o[2 * G + g] = hi; o[3 * G + g] = lo; o[4 * G + g] = hi; o[5 * G + g] = mid;
+        }
+        if (g == 0)
+            for (int e = 6 * G + lane; e < 6 * G + gpad; e += 32) o[e] = 0;
+    }
+}
+
 }  // namespace q4b
 
 using namespace q4b;
@@ -370,6 +441,43 @@ extern "C" int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t l
     Q4B_LAUNCH_CHECK();
     dim3 grid2((unsigned)ceil_div(N, ADD_COLS), (unsigned)ceil_div(M, ADD_ROWS));
     int4g_addend_kernel<<<grid2, 256, 0, st>>>(rowsums_ws, M, corr, bias, N, (int)G, addend_out);
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_int4g_fold_ktiles(int64_t K, int64_t group) {
+    if (K < 1 || group < 1) return 0;
+    return (int)ceil_div(6 * ceil_div(K, group), TILE_K);
+}
+
+extern "C" int q4b_int4g_fold_operand(const float *corr, int64_t K, int64_t N, int64_t group, void *operand_out, void *stream) {
+    if (corr == nullptr || operand_out == nullptr) return Q4B_ERR_ARG;
+    if (int rc = check_g(K, N, group)) return rc;
+    if (!aligned(operand_out, 16)) return Q4B_ERR_ALIGN;
+    const int64_t G = ceil_div(K, group);
+    const int E = q4b_int4g_fold_ktiles(K, group) * TILE_K;
+    const int64_t threads = (G + 1) * N;                          // one more "group" of threads clears the padding
+    int4g_fold_operand_kernel<<<(unsigned)ceil_div(threads, 256), 256, 0, (cudaStream_t)stream>>>(corr, (int)G, N, E, (uint16_t *)operand_out);
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_int4g_fold_rows(const void *x, int x_dtype, int64_t M, int64_t ldx, int64_t K, int64_t group, void *rows_out,
+                                   void *stream) {
+    if (x == nullptr || rows_out == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || ldx < K || K < 1 || group < 1) return Q4B_ERR_ARG;
+    if (!aligned(rows_out, 16)) return Q4B_ERR_ALIGN;
+    const int64_t G = ceil_div(K, group);
+    if (G > 65535) return Q4B_ERR_SHAPE;
+    const int E = q4b_int4g_fold_ktiles(K, group) * TILE_K;
+    const int64_t pairs = M * G;
+    const unsigned grid = (unsigned)(ceil_div(pairs, 8) < 16384 ? ceil_div(pairs, 8) : 16384);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case Q4B_F16: int4g_fold_rows_kernel<__half><<<grid, 256, 0, st>>>((const __half *)x, M, ldx, K, group, (int)G, E, (uint16_t *)rows_out); break;
+        case Q4B_BF16: int4g_fold_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)x, M, ldx, K, group, (int)G, E, (uint16_t *)rows_out); break;
+        default: return Q4B_ERR_DTYPE;
+    }
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
 }

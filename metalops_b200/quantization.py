@@ -326,10 +326,13 @@ class Int4GPrepacked:
     """A group-wise INT4 weight converted for the matmul kernels: streaming tiles (block scale =
     fp16 of the group scale) plus the fp32 per-group constant ``8*d - zero*scale``."""
 
-    __slots__ = ("tiles", "corr", "group_size")
+    __slots__ = ("tiles", "corr", "group_size", "fold", "fold_ktiles")
 
-    def __init__(self, tiles: Q4Prepacked, corr: torch.Tensor, group_size: int):
+    def __init__(self, tiles: Q4Prepacked, corr: torch.Tensor, group_size: int, fold: torch.Tensor, fold_ktiles: int):
         self.tiles, self.corr, self.group_size = tiles, corr, group_size
+        # corr as the bf16 operand [N, 64 * fold_ktiles] of the extra k-tiles that carry the zero-point
+        # term inside the prefill kernel's contraction (three-way bf16 split, six products)
+        self.fold, self.fold_ktiles = fold, fold_ktiles
 
 
 def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int = 128) -> Int4GPrepacked:
@@ -357,7 +360,13 @@ def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
     if bad.value:
         raise RuntimeError("prepack_int4: a group scale is outside float16's range (or NaN); the fused INT4 kernels "
                            "store block scales as float16")
-    out = Int4GPrepacked(Q4Prepacked(tiles, K, N), corr, group_size)
+    lib = _cabi.load()
+    kx = lib.q4b_int4g_fold_ktiles(K, group_size)
+    fold = torch.empty((N, 64 * kx), dtype=torch.bfloat16, device=p.device)
+    with torch.cuda.device(p.device):
+        _cabi.check(lib.q4b_int4g_fold_operand(corr.data_ptr(), K, N, group_size, fold.data_ptr(), _cabi.stream_ptr(p.device)),
+                    "prepack_int4")
+    out = Int4GPrepacked(Q4Prepacked(tiles, K, N), corr, group_size, fold, kx)
     try:
         W_packed._q4b_int4g = (key, out)
     except AttributeError:
@@ -366,6 +375,7 @@ def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
 
 
 _ACT_FLAGS = {None: 0, "none": 0, "silu": _cabi.FLAG_ACT_SILU, "gelu": _cabi.FLAG_ACT_GELU}
+_FOLD_MIN_ROWS = 128        # above: the prefill kernel with the zero-point term folded in; up to it: the fp32 addend
 
 
 def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None,
@@ -379,12 +389,26 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
     assert x.shape[1] == K, f"X K dim ({x.shape[1]}) must match weight K ({K})"
     if M == 0:
         return torch.empty((0, N), dtype=in_dtype, device=x.device)
-    addend = torch.empty((M, N), dtype=torch.float32, device=x.device)
     lib = _cabi.load()
-    rowsums = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, pre.group_size) // 4, dtype=torch.float32, device=x.device)
     b32 = None
     if bias is not None:
         b32 = bias.to(device=x.device, dtype=torch.float32).contiguous()
+    if M > _FOLD_MIN_ROWS:
+        # prefill: the zero-point term rides in the contraction as extra k-tiles, no [M, N] addend
+        rows = torch.empty((M, 64 * pre.fold_ktiles), dtype=torch.bfloat16, device=x.device)
+        y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            sp = _cabi.stream_ptr(x.device)
+            rc = lib.q4b_int4g_fold_rows(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), K, pre.group_size, rows.data_ptr(), sp)
+            _cabi.check(rc, "matmul_int4")
+            rc = lib.q4b_int4g_gemm_fold(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.tiles.data.data_ptr(), K, N,
+                                         pre.fold.data_ptr(), rows.data_ptr(), pre.fold_ktiles,
+                                         b32.data_ptr() if b32 is not None else None, y.data_ptr(), y.stride(0),
+                                         _ACT_FLAGS[activation], sp)
+        _cabi.check(rc, "matmul_int4")
+        return y.float() if in_dtype == torch.float32 else y
+    addend = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    rowsums = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, pre.group_size) // 4, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         rc = lib.q4b_int4g_addend(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.corr.data_ptr(),
                                   b32.data_ptr() if b32 is not None else None, K, N, pre.group_size,
