@@ -90,7 +90,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     const int items = panels * row_tiles;
     // Folded rank-G term (GENERAL only): KX further k-tiles whose A operand is read as bf16 from corr_op
     // [N, 64 KX] and whose X slices come from a second tensor map (bf16 [M, 64 KX]); KT counts all k-tiles.
-    const int KT = KU + (GENERAL ? KX : 0);
+    // They come first in an item, so that their operand loads (global memory, not the ring) pass while the
+    // previous item's accumulator is still being read out.
+    const int KF = GENERAL ? KX : 0;                                       // k-tiles of the folded term, first in every item
+    const int KT = KU + KF;
     const int spi = (KT + STAGE_STEPS - 1) / STAGE_STEPS;                  // stages per item
 
     if (threadIdx.x == 0) {
@@ -126,17 +129,18 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             for (int q = 0; q < spi; ++q, ++gq) {
                 const int slot = gq % NSTAGE_W, fill = gq / NSTAGE_W;
                 if (!mbar_wait_warp(bar_empty_w(slot), (fill & 1) ^ 1, abort_flag, &g_status, 601)) goto done;
-                const int nreg = max(0, min(STAGE_STEPS, KU - q * STAGE_STEPS));        // packed k-tiles of the stage
-                const uint32_t bytes = (uint32_t)(nreg * TILE_BYTES);
-                if (nreg == 0) {                          // a stage of the folded term only: nothing to copy
+                // the item's k-tiles: first the KF tiles of the folded term (nothing to copy), then the packed ones
+                const int t0 = max(q * STAGE_STEPS, KF), t1 = min(q * STAGE_STEPS + STAGE_STEPS, KT);   // packed tiles of the stage: [t0, t1)
+                if (t1 <= t0) {
                     if (lane == 0) mbar_arrive(bar_full_w(slot, fill));
                     continue;
                 }
+                const uint32_t bytes = (uint32_t)((t1 - t0) * TILE_BYTES);
                 if (lane == 0) mbar_arrive_expect_tx(bar_full_w(slot, fill), (uint32_t)valid * bytes);
                 __syncwarp();
                 if (lane < valid)
-                    bulk_load(base + SMEM_RING + slot * W_STAGE_BYTES + lane * TILE_RUN_BYTES, src + (size_t)q * TILE_RUN_BYTES, bytes,
-                              bar_full_w(slot, fill));
+                    bulk_load(base + SMEM_RING + slot * W_STAGE_BYTES + lane * TILE_RUN_BYTES + (t0 - q * STAGE_STEPS) * TILE_BYTES,
+                              src + (size_t)(t0 - KF) * TILE_BYTES, bytes, bar_full_w(slot, fill));
             }
         }
     } else if (warp == WARP_X) {
@@ -153,8 +157,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     for (int j = 0; j < nk; ++j) {
                         const int tile = q * STAGE_STEPS + j;
                         const uint32_t dst = base + SMEM_X + s * X_STAGE_BYTES + j * X_TILE_BYTES;
-                        if (tile < KU) tma_load_2d(dst, &tmap_x, tile * TILE_K, row0, bar_full(s));
-                        else tma_load_2d(dst, &tmap_r, (tile - KU) * TILE_K, row0, bar_full(s));
+                        if (tile >= KF) tma_load_2d(dst, &tmap_x, (tile - KF) * TILE_K, row0, bar_full(s));
+                        else tma_load_2d(dst, &tmap_r, tile * TILE_K, row0, bar_full(s));
                     }
                 }
             }
@@ -177,8 +181,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 if (elect_one()) {
                     const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_X + s * X_STAGE_BYTES);
                     const uint32_t a0 = tmem_base + (uint32_t)(A_COL0 + s * STAGE_STEPS * 32);
-                    const uint32_t id0 = q * STAGE_STEPS < KU ? idesc : idesc_fold;
-                    const uint32_t id1 = q * STAGE_STEPS + 1 < KU ? idesc : idesc_fold;
+                    const uint32_t id0 = q * STAGE_STEPS >= KF ? idesc : idesc_fold;
+                    const uint32_t id1 = q * STAGE_STEPS + 1 >= KF ? idesc : idesc_fold;
 #pragma unroll
                     for (int k = 0; k < TILE_K / 16; ++k)
                         tc_mma_ts_f16(tmem_base + D_COL0, a0 + k * 8, bdesc + 2 * k, id0, (uint32_t)((q | k) != 0));
@@ -311,12 +315,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 if (!mbar_wait_warp(bar_empty(s), ((gq / ST) & 1) ^ 1, abort_flag, &g_status, 608)) goto done;
                 tc_fence_after();
                 const uint32_t a_addr = lane_taddr + (uint32_t)(A_COL0 + (s * STAGE_STEPS + sub) * 32);
-                if (!GENERAL || i < KU) {
+                if (!GENERAL || i >= KF) {
                     dequant_tile_to_tmem<BF16>(base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES, woff, doff, a_addr);
                 } else {
                     // a k-tile of the folded term: this thread's column of corr_op, 64 bf16 = 2 x 16 words
                     const int64_t n = (int64_t)(item % panels) * PANEL_N + wq * 32 + lane;
-                    const uint4 *src = reinterpret_cast<const uint4 *>(corr_op + (size_t)n * (size_t)(KX * TILE_K) + (size_t)(i - KU) * TILE_K);
+                    const uint4 *src = reinterpret_cast<const uint4 *>(corr_op + (size_t)n * (size_t)(KX * TILE_K) + (size_t)i * TILE_K);
 #pragma unroll
                     for (int kb = 0; kb < 2; ++kb) {
                         uint32_t regs[16];

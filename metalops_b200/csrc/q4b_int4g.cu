@@ -148,6 +148,27 @@ int4g_corr_kernel(const TS *__restrict__ scales, const TS *__restrict__ zeros, i
 //                        are broadcast from shared memory (one 16-byte read of four rows feeds four
 //                        two-wide FMAs, fma.rn.f32x2), 2 x 32 accumulators per thread, coalesced fp32 stores.  corr is re-read once per row
 //                        tile, from L2.
+// Sum of x[k0 .. k1) over the warp, the same value on every lane, in a fixed order.  When the group is
+// 128 sixteen-bit values and 16-byte aligned, sixteen lanes read it with one 16-byte load each (lanes 16-31
+// repeat the loads of lanes 0-15 and take no part in the sum).
+template <typename TX>
+__device__ __forceinline__ float warp_group_sum(const TX *xr, int64_t k0, int64_t k1, int lane) {
+    float s = 0.0f;
+    if (sizeof(TX) == 2 && k1 - k0 == 128 && (reinterpret_cast<uintptr_t>(xr + k0) & 15) == 0) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xr + k0) + (lane & 15));
+        const TX *e = reinterpret_cast<const TX *>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += Num<TX>::r((float)e[i]);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        return s;
+    }
+    for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return s;
+}
+
 template <typename TX>
 __global__ void __launch_bounds__(256)
 int4g_rowsum_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t K, int64_t group, int G, float *__restrict__ rowsums) {
@@ -165,10 +186,7 @@ int4g_rowsum_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t K,
         }
         const TX *xr = x + m * ldx;
         const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
-        float s = 0.0f;
-        for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float s = warp_group_sum<TX>(xr, k0, k1, lane);
         if (lane == 0) rowsums[p] = s;
     }
 }
@@ -286,13 +304,18 @@ int4g_fold_operand_kernel(const float *__restrict__ corr, int G, int64_t N, int 
     o[0] = hi; o[G] = hi; o[2 * G] = mid; o[3 * G] = hi; o[4 * G] = lo; o[5 * G] = mid;
 }
 
-// rows [M, E] bf16 from X: a warp per (row, group) as in int4g_rowsum_kernel, same summation order.
+// rows [M, E] bf16 from X.  Generic form: a warp per (row, group) as in int4g_rowsum_kernel.
+__device__ __forceinline__ void store_fold_row_terms(uint16_t *o, int G, int g, float s) {
+    uint16_t hi, mid, lo;
+    split3_bf16(s, hi, mid, lo);
+    o[g] = hi; o[G + g] = mid; o[2 * G + g] = hi; o[3 * G + g] = lo; o[4 * G + g] = hi; o[5 * G + g] = mid;
+}
+
 template <typename TX>
 __global__ void __launch_bounds__(256)
 int4g_fold_rows_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t K, int64_t group, int G, int E,
                        uint16_t *__restrict__ rows_out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int gpad = (E - 6 * G + 0);                            // zeros to write per row, by the row's first warp
     const int64_t pairs = M * G;
     for (int64_t p = (int64_t)blockIdx.x * 8 + warp; p < pairs; p += (int64_t)gridDim.x * 8) {
         int64_t m;
@@ -304,20 +327,49 @@ int4g_fold_rows_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int64_t
             m = p / G;
             g = (int)(p % G);
         }
-        const TX *xr = x + m * ldx;
         const int64_t k0 = (int64_t)g * group, k1 = min(k0 + group, K);
-        float s = 0.0f;
-        for (int64_t k = k0 + lane; k < k1; k += 32) s += Num<TX>::ld(xr + k);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float s = warp_group_sum<TX>(x + m * ldx, k0, k1, lane);
         uint16_t *o = rows_out + m * E;
-        if (lane == 0) {
-            uint16_t hi, mid, lo;
-            split3_bf16(s, hi, mid, lo);
-            o[g] = hi; o[G + g] = mid; o[2 * G + g] = hi; o[3 * G + g] = lo; o[4 * G + g] = hi; o[5 * G + g] = mid;
-        }
+        if (lane == 0) store_fold_row_terms(o, G, g, s);
         if (g == 0)
-            for (int e = 6 * G + lane; e < 6 * G + gpad; e += 32) o[e] = 0;
+            for (int e = 6 * G + lane; e < E; e += 32) o[e] = 0;
+    }
+}
+
+// Groups of 128 sixteen-bit values, rows 16-byte aligned, K a multiple of 128: a warp takes sixteen
+// consecutive groups of a row (4 KB): eight 16-byte loads per lane in flight, half-warp reductions, then
+// lanes 0..15 each split one group sum and store its six terms (consecutive lanes, consecutive addresses).
+template <typename TX>
+__global__ void __launch_bounds__(256)
+int4g_fold_rows128_kernel(const TX *__restrict__ x, int64_t M, int64_t ldx, int G, int E, uint16_t *__restrict__ rows_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = (G + 15) / 16;                            // warps per row
+    const int64_t units = M * chunks;
+    for (int64_t u = (int64_t)blockIdx.x * 8 + warp; u < units; u += (int64_t)gridDim.x * 8) {
+        const int64_t m = u / chunks;
+        const int g0 = (int)(u % chunks) * 16;
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + m * ldx + (int64_t)g0 * 128);
+        uint4 v[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            v[t] = g0 + 2 * t + (lane >> 4) < G ? __ldg(src + t * 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
+        float mine = 0.0f;                                       // lane l < 16 ends up with the sum of group g0 + l
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            const TX *e = reinterpret_cast<const TX *>(&v[t]);
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s += Num<TX>::r((float)e[i]);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const float lo_half = __shfl_sync(0xffffffffu, s, 0), hi_half = __shfl_sync(0xffffffffu, s, 16);
+            if (lane == 2 * t) mine = lo_half;
+            if (lane == 2 * t + 1) mine = hi_half;
+        }
+        uint16_t *o = rows_out + m * E;
+        if (lane < 16 && g0 + lane < G) store_fold_row_terms(o, G, g0 + lane, mine);
+        if (g0 == 0)
+            for (int e = 6 * G + lane; e < E; e += 32) o[e] = 0;
     }
 }
 
@@ -473,6 +525,17 @@ extern "C" int q4b_int4g_fold_rows(const void *x, int x_dtype, int64_t M, int64_
     const int64_t pairs = M * G;
     const unsigned grid = (unsigned)(ceil_div(pairs, 8) < 16384 ? ceil_div(pairs, 8) : 16384);
     cudaStream_t st = (cudaStream_t)stream;
+    if (group == 128 && K % 128 == 0 && ldx % 8 == 0 && aligned(x, 16)) {
+        const int64_t units = M * ceil_div(G, 16);
+        const unsigned grid128 = (unsigned)(ceil_div(units, 8) < 16384 ? ceil_div(units, 8) : 16384);
+        switch (x_dtype) {
+            case Q4B_F16: int4g_fold_rows128_kernel<__half><<<grid128, 256, 0, st>>>((const __half *)x, M, ldx, (int)G, E, (uint16_t *)rows_out); break;
+            case Q4B_BF16: int4g_fold_rows128_kernel<__nv_bfloat16><<<grid128, 256, 0, st>>>((const __nv_bfloat16 *)x, M, ldx, (int)G, E, (uint16_t *)rows_out); break;
+            default: return Q4B_ERR_DTYPE;
+        }
+        Q4B_LAUNCH_CHECK();
+        return Q4B_OK;
+    }
     switch (x_dtype) {
         case Q4B_F16: int4g_fold_rows_kernel<__half><<<grid, 256, 0, st>>>((const __half *)x, M, ldx, K, group, (int)G, E, (uint16_t *)rows_out); break;
         case Q4B_BF16: int4g_fold_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16 *)x, M, ldx, K, group, (int)G, E, (uint16_t *)rows_out); break;
