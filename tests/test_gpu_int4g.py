@@ -255,3 +255,40 @@ def test_addend_many_rows_and_ragged_tiles(mo, cuda_dev):
         ref = x.float().view(M, G, group).sum(-1) @ corr + bias
         assert torch.allclose(out, ref, rtol=1e-4, atol=1e-4), (M, K, N, float((out - ref).abs().max()))
     assert lib.q4b_int4g_addend(x.data_ptr(), _cabi.F16, 1, 4096, corr.data_ptr(), None, 4096, 1000, 32, None, out.data_ptr(), None) == _cabi.ERR_ARG
+
+
+@pytest.mark.parametrize("M,K,N,gs,xdtype,shift", [
+    (300, 256, 200, 128, torch.float16, 0.0),
+    (129, 4096, 1000, 128, torch.bfloat16, 0.05),       # zero points far from 8: the term is 15 x the main product
+    (513, 2080, 520, 32, torch.float16, 0.08),          # odd number of k-tiles, seven fold tiles
+    (2048, 4096, 264, 128, torch.bfloat16, 0.0),
+])
+def test_folded_zero_point_term_matches_the_addend_path(mo, cuda_dev, M, K, N, gs, xdtype, shift):
+    """Above 128 rows matmul_int4 carries the zero-point term inside the contraction (extra k-tiles, bf16
+    three-way splits).  It must agree with the fp32-addend path to a unit of the output type, and with
+    the fp64 product of the dequantised weight like that path does; bias and activation included."""
+    from metalops_b200 import quantization as Q
+    g = torch.Generator().manual_seed(M + K)
+    w = (torch.randn(K, N, generator=g) * 0.02 + shift).half().to(cuda_dev)
+    x = (torch.randn(M, K, generator=g).abs() * 0.5 + 0.1).to(xdtype).to(cuda_dev)      # a positive mean: a large term
+    bias = torch.randn(N, generator=g).to(cuda_dev)
+    p, s, z = mo.quantize_int4(w, gs)
+    ref = x.double() @ mo.dequantize_int4(p, s, z, gs).double()
+    pre = Q.prepack_int4(p, s, z, gs)
+    assert pre.fold_ktiles == (6 * (K // gs) + 63) // 64
+    y_fold = Q._matmul_int4_prepacked(x, pre)
+    yb_fold = Q._matmul_int4_prepacked(x, pre, bias=bias, activation="silu")
+    assert Q.wait_status(cuda_dev) == 0
+    keep = Q._FOLD_MIN_ROWS
+    try:
+        Q._FOLD_MIN_ROWS = 1 << 30
+        y_add = Q._matmul_int4_prepacked(x, pre)
+        yb_add = Q._matmul_int4_prepacked(x, pre, bias=bias, activation="silu")
+    finally:
+        Q._FOLD_MIN_ROWS = keep
+    e_fold, e_add = orc.rel_l2(y_fold, ref.float()), orc.rel_l2(y_add, ref.float())
+    assert e_fold <= max(1.05 * e_add, 1e-4), (e_fold, e_add)
+    ulp = 2.0 ** (-7 if xdtype == torch.bfloat16 else -10)
+    assert float(((y_fold.float() - y_add.float()).abs() / y_add.float().abs().clamp_min(1.0)).max()) <= 2 * ulp
+    assert float(((yb_fold.float() - yb_add.float()).abs() / yb_add.float().abs().clamp_min(1.0)).max()) <= 2 * ulp
+    assert torch.equal(y_fold, Q._matmul_int4_prepacked(x, pre)), "two runs differ bitwise"
