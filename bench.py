@@ -712,7 +712,7 @@ def bench_groupwise_int4(dev, stream, lib, peaks):
         def full(i, M=M, x=x, y=y, adds=adds, rs=rs, rows=rows):
             sp = torch.cuda.current_stream(dev).cuda_stream
             p = sets[i % 4]
-            if M > 128:        # prefill: the zero-point term folded into the contraction (what matmul_int4 does)
+            if M > 16:         # tensor-core kernels: the zero-point term folded into the contraction (what matmul_int4 does)
                 rc = lib.q4b_int4g_fold_rows(x.data_ptr(), _cabi.BF16, M, K, K, G, rows.data_ptr(), sp)
                 rc = rc or lib.q4b_int4g_gemm_fold(x.data_ptr(), _cabi.BF16, M, K, p.tiles.data.data_ptr(), K, N, p.fold.data_ptr(),
                                                    rows.data_ptr(), p.fold_ktiles, None, y.data_ptr(), N, 0, sp)

@@ -198,8 +198,8 @@ Q4B_API int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx,
                              const float *bias, int64_t K, int64_t N, int64_t group, float *rowsums_ws,
                              float *addend_out, void *stream);
 /*
- * The zero-point term folded into the contraction, for the persistent prefill kernel: instead of an
- * [M, N] fp32 addend, KX = q4b_int4g_fold_ktiles(K, group) further k-tiles multiply
+ * The zero-point term folded into the contraction of the tensor-core kernels (those behind q4b_gemm,
+ * picked by M in the same way): instead of an [M, N] fp32 addend, KX = q4b_int4g_fold_ktiles(K, group) further k-tiles multiply
  *   fold_rows    [M, 64 KX] bf16, from X per call (q4b_int4g_fold_rows: the rows' group sums), by
  *   fold_operand [N, 64 KX] bf16, from corr once per weight (q4b_int4g_fold_operand).
  * Both factors are split into three bf16 terms and the six largest products kept, so the term keeps

@@ -17,7 +17,8 @@ namespace q4b {
 
 int device_sm_count();
 int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
-                     const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st);
+                     const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st,
+                     const void *corr_op = nullptr, const void *xr = nullptr, int KX = 0);
 int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N, const float *addend,
                    int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st, const void *corr_op = nullptr,
                    const void *xr = nullptr, int KX = 0);
@@ -101,8 +102,8 @@ extern "C" int q4b_gemm_wt_addend(const void *x, int x_dtype, int64_t M, int64_t
     return gemm_wt_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, (cudaStream_t)stream);
 }
 
-// The group-wise INT4 product with its zero-point term folded into the contraction (persistent prefill
-// kernel, any M >= 1): KX further k-tiles multiply fold_rows [M, 64 KX] by fold_operand [N, 64 KX] (both
+// The group-wise INT4 product with its zero-point term folded into the contraction (the kernels behind
+// q4b_gemm, picked by M as there; any M >= 1): KX further k-tiles multiply fold_rows [M, 64 KX] by fold_operand [N, 64 KX] (both
 // bf16, from q4b_int4g_fold_rows / q4b_int4g_fold_operand).  bias: one fp32 row of N values, or NULL.
 extern "C" int q4b_int4g_gemm_fold(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
                                    const void *fold_operand, const void *fold_rows, int KX, const float *bias, void *y,
@@ -110,6 +111,9 @@ extern "C" int q4b_int4g_gemm_fold(const void *x, int x_dtype, int64_t M, int64_
     if (int rc = check_gemm_args(x, x_dtype, M, ldx, prepacked, K, N, bias, 0, y, ldy, flags)) return rc;
     if (fold_operand == nullptr || fold_rows == nullptr || KX < 1 || KX > 4096) return Q4B_ERR_ARG;
     if (!aligned(fold_operand, 16) || !aligned(fold_rows, 16)) return Q4B_ERR_ALIGN;
+    if (M <= 128 && ceil_div(tiles_n(N), 8) <= 2 * device_sm_count())
+        return gemm_tmem_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, bias, 0, y, ldy, flags, (cudaStream_t)stream,
+                                fold_operand, fold_rows, KX);
     return gemm_wt_launch(x, x_dtype == Q4B_BF16, (int)M, ldx, prepacked, K, N, bias, 0, y, ldy, flags, (cudaStream_t)stream,
                           fold_operand, fold_rows, KX);
 }

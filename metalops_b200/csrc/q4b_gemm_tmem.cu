@@ -58,7 +58,8 @@ __device__ int g_status = 0;
 
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 2)
-gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__restrict__ prepacked, int M, int64_t K,
+gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_r,
+                 const uint8_t *__restrict__ prepacked, const uint16_t *__restrict__ corr_op, int KF, int M, int64_t K,
                  int64_t N, uint16_t *__restrict__ y, int64_t ldy, const float *__restrict__ addend, int64_t ld_add, int KS,
                  int rows, int act) {
     extern __shared__ uint8_t smem_raw[];
@@ -84,7 +85,11 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
     const int panel = (int)blockIdx.x / KS, ks = (int)blockIdx.x % KS;    // ks = rank in the cluster
     const int nt0 = panel * PANEL_TILES;
     const int valid = min(PANEL_TILES, NT - nt0);                          // column tiles that exist
-    const int ku0 = (int)((int64_t)KU * ks / KS), ku1 = (int)((int64_t)KU * (ks + 1) / KS);
+    // k-tiles of the product: first the KF tiles of the group-wise format's folded zero-point term (A operand
+    // read as bf16 from corr_op [N, 64 KF], X side through tmap_r: bf16 [M, 64 KF]; KF = 0: none), then the
+    // KU packed ones.  The cluster splits all of them.
+    const int KT = KF + KU;
+    const int ku0 = (int)((int64_t)KT * ks / KS), ku1 = (int)((int64_t)KT * (ks + 1) / KS);
     const int nsteps = ku1 - ku0;                                          // k-tiles of this CTA
     const int nstages = (nsteps + STAGE_STEPS - 1) / STAGE_STEPS;
 
@@ -108,16 +113,22 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
 
     if (warp == WARP_W) {
         // ---------------- packed-weight producer: lane t copies column tile t's run of the stage ----------------
-        const uint8_t *src = prepacked + tile_offset(nt0 + min(lane, valid - 1), ku0, KU);
+        const uint8_t *src = prepacked + tile_offset(nt0 + min(lane, valid - 1), 0, KU);
         for (int q = 0; q < nstages; ++q) {
             const int slot = q % NSTAGE;
             if (!mbar_wait_warp(bar_empty_w(slot), ((q / NSTAGE) & 1) ^ 1, abort_flag, &g_status, 401)) goto done;
-            const uint32_t bytes = (uint32_t)(min(STAGE_STEPS, nsteps - q * STAGE_STEPS) * TILE_BYTES);
+            const int s0 = ku0 + q * STAGE_STEPS;                          // first k-tile of the stage
+            const int t0 = max(s0, KF), t1 = min(s0 + STAGE_STEPS, ku1);   // its packed k-tiles: [t0, t1)
+            if (t1 <= t0) {                                                // folded-term tiles only: nothing to copy
+                if (lane == 0) mbar_arrive(bar_full_w(slot));
+                continue;
+            }
+            const uint32_t bytes = (uint32_t)((t1 - t0) * TILE_BYTES);
             if (lane == 0) mbar_arrive_expect_tx(bar_full_w(slot), (uint32_t)valid * bytes);
             __syncwarp();
             if (lane < valid)
-                bulk_load(base + SMEM_RING + slot * STAGE_BYTES + lane * TILE_RUN_BYTES, src + (size_t)q * TILE_RUN_BYTES, bytes,
-                          bar_full_w(slot));
+                bulk_load(base + SMEM_RING + slot * STAGE_BYTES + lane * TILE_RUN_BYTES + (t0 - s0) * TILE_BYTES,
+                          src + (size_t)(t0 - KF) * TILE_BYTES, bytes, bar_full_w(slot));
         }
     } else if (warp == WARP_X) {
         // ---------------- X producer (x depends on earlier kernels of the stream; the weights do not) ----------------
@@ -127,14 +138,17 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
                 const int s = i % SX;
                 if (!mbar_wait(bar_x_empty(s), ((i / SX) & 1) ^ 1, abort_flag, &g_status, 402)) goto done;
                 mbar_arrive_expect_tx(bar_x_full(s), (uint32_t)(rows * TILE_K * 2));
-                tma_load_2d(base + SMEM_X + s * X_STAGE_BYTES, &tmap_x, (ku0 + i) * TILE_K, 0, bar_x_full(s));
+                const int t = ku0 + i;
+                if (t >= KF) tma_load_2d(base + SMEM_X + s * X_STAGE_BYTES, &tmap_x, (t - KF) * TILE_K, 0, bar_x_full(s));
+                else tma_load_2d(base + SMEM_X + s * X_STAGE_BYTES, &tmap_r, t * TILE_K, 0, bar_x_full(s));
             }
         }
     } else if (warp == WARP_MMA) {
         // ---------------- MMA issuer: converged warp, one elected lane issues ----------------
-        const uint32_t idesc = make_idesc(BF16, PANEL_N, rows);
+        const uint32_t idesc = make_idesc(BF16, PANEL_N, rows), idesc_fold = make_idesc(true, PANEL_N, rows);   // the folded term is bf16
         for (int i = 0; i < nsteps; ++i) {
             const int st = i % TM_STAGES, xs = i % SX;
+            const uint32_t id = ku0 + i >= KF ? idesc : idesc_fold;
             if (!mbar_wait_warp(bar_a_full(st), (i / TM_STAGES) & 1, abort_flag, &g_status, 403)) goto done;
             if (!mbar_wait_warp(bar_x_full(xs), (i / SX) & 1, abort_flag, &g_status, 404)) goto done;
             tc_fence_after();
@@ -142,7 +156,7 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
                 const uint64_t bdesc = make_kmajor_sw128_desc(base + SMEM_X + xs * X_STAGE_BYTES);
 #pragma unroll
                 for (int k = 0; k < TILE_K / 16; ++k)
-                    tc_mma_ts_f16(tmem_base + D_COL0, tmem_base + (uint32_t)(A_COL0 + st * 32 + k * 8), bdesc + 2 * k, idesc,
+                    tc_mma_ts_f16(tmem_base + D_COL0, tmem_base + (uint32_t)(A_COL0 + st * 32 + k * 8), bdesc + 2 * k, id,
                                   (uint32_t)((i | k) != 0));
                 tc_commit(bar_a_empty(st));
                 tc_commit(bar_x_empty(xs));
@@ -167,8 +181,24 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t *__re
             if (!mbar_wait_warp(bar_full_w(slot), (q / NSTAGE) & 1, abort_flag, &g_status, 405)) goto done;
             if (!mbar_wait_warp(bar_a_empty(st), ((i / TM_STAGES) & 1) ^ 1, abort_flag, &g_status, 406)) goto done;
             tc_fence_after();
-            dequant_tile_to_tmem<BF16>(base + SMEM_RING + slot * STAGE_BYTES + (i % STAGE_STEPS) * TILE_BYTES, woff, doff,
-                                       lane_taddr + (uint32_t)(A_COL0 + st * 32));
+            const uint32_t a_addr = lane_taddr + (uint32_t)(A_COL0 + st * 32);
+            if (ku0 + i >= KF) {
+                dequant_tile_to_tmem<BF16>(base + SMEM_RING + slot * STAGE_BYTES + (i % STAGE_STEPS) * TILE_BYTES, woff, doff, a_addr);
+            } else {
+                // a k-tile of the folded term: this thread's column of corr_op, 64 bf16 = 2 x 16 words
+                const int64_t n = (int64_t)nt0 * TILE_N + wq * 32 + lane;
+                const uint4 *src = reinterpret_cast<const uint4 *>(corr_op + (size_t)n * (size_t)(KF * TILE_K) + (size_t)(ku0 + i) * TILE_K);
+#pragma unroll
+                for (int kb = 0; kb < 2; ++kb) {
+                    uint32_t regs[16];
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        const uint4 t = n < N ? __ldg(src + kb * 4 + v4) : make_uint4(0u, 0u, 0u, 0u);
+                        regs[4 * v4] = t.x; regs[4 * v4 + 1] = t.y; regs[4 * v4 + 2] = t.z; regs[4 * v4 + 3] = t.w;
+                    }
+                    tc_st_32x32b_x16(a_addr + (uint32_t)(kb * 16), regs);
+                }
+            }
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -258,8 +288,9 @@ static int choose_ksplit(int64_t panels, int64_t KU, int sms) {
 }
 
 template <bool BF16>
-static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t K, int64_t N, void *y, int64_t ldy,
-                  const float *addend, int64_t ld_add, int rows, int act, int flags, int sms, cudaStream_t st) {
+static int launch(const CUtensorMap &tmap, const CUtensorMap &tmap_r, const void *prepacked, const void *corr_op, int KF, int M,
+                  int64_t K, int64_t N, void *y, int64_t ldy, const float *addend, int64_t ld_add, int rows, int act, int flags,
+                  int sms, cudaStream_t st) {
     {   // opt in to the large dynamic shared memory once per device and instantiation
         static bool attr_done[64] = {};
         static std::mutex attr_mu;
@@ -272,7 +303,7 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t
         }
     }
     const int64_t panels = ceil_div(tiles_n(N), PANEL_TILES);
-    int ks = choose_ksplit(panels, tiles_k(K), sms);
+    int ks = choose_ksplit(panels, tiles_k(K) + KF, sms);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(panels * ks));
     cfg.blockDim = dim3(THREADS);
@@ -294,8 +325,8 @@ static int launch(const CUtensorMap &tmap, const void *prepacked, int M, int64_t
     }
     cfg.attrs = attr;
     cfg.numAttrs = (unsigned)na;
-    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tmem_kernel<BF16>, tmap, (const uint8_t *)prepacked, M, K, N, (uint16_t *)y, ldy,
-                                    addend, ld_add, ks, rows, act));
+    Q4B_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tmem_kernel<BF16>, tmap, tmap_r, (const uint8_t *)prepacked, (const uint16_t *)corr_op, KF,
+                                    M, K, N, (uint16_t *)y, ldy, addend, ld_add, ks, rows, act));
     return Q4B_OK;
 }
 
@@ -305,15 +336,22 @@ int device_sm_count();
 
 // Arguments as checked by the matmul entry points; 1 <= M <= 128.
 int gemm_tmem_launch(const void *x, int bf16, int M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
-                     const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st) {
+                     const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags, cudaStream_t st, const void *corr_op,
+                     const void *xr, int KX) {
     if (M < 1 || M > gemmtm::MAX_ROWS) return Q4B_ERR_SHAPE;
     const int rows = (M + 15) / 16 * 16;                                   // the MMA's N: a multiple of 16
-    CUtensorMap tmap;
+    CUtensorMap tmap, tmap_r;
     if (int rc = encode_x_tensor_map(&tmap, x, bf16, M, K, ldx, rows)) return rc;       // 64 k x `rows` rows per copy
+    const bool fold = corr_op != nullptr && xr != nullptr && KX > 0;       // the group-wise format's folded term
+    if (fold) {
+        if (int rc = encode_x_tensor_map(&tmap_r, xr, 1, M, (int64_t)KX * TILE_K, (int64_t)KX * TILE_K, rows)) return rc;
+    } else {
+        tmap_r = tmap;
+    }
     const int sms = device_sm_count();
     const int act = act_of_flags(flags);
-    return bf16 ? gemmtm::launch<true>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, flags, sms, st)
-                : gemmtm::launch<false>(tmap, prepacked, M, K, N, y, ldy, addend, ld_add, rows, act, flags, sms, st);
+    return bf16 ? gemmtm::launch<true>(tmap, tmap_r, prepacked, corr_op, fold ? KX : 0, M, K, N, y, ldy, addend, ld_add, rows, act, flags, sms, st)
+                : gemmtm::launch<false>(tmap, tmap_r, prepacked, corr_op, fold ? KX : 0, M, K, N, y, ldy, addend, ld_add, rows, act, flags, sms, st);
 }
 
 // read and clear this file's wait status (host side; the caller has synchronised the stream)

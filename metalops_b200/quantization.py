@@ -375,7 +375,7 @@ def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
 
 
 _ACT_FLAGS = {None: 0, "none": 0, "silu": _cabi.FLAG_ACT_SILU, "gelu": _cabi.FLAG_ACT_GELU}
-_FOLD_MIN_ROWS = 128        # above: the prefill kernel with the zero-point term folded in; up to it: the fp32 addend
+_FOLD_MIN_ROWS = 16         # above: the tensor-core kernels with the zero-point term folded in; up to it: the fp32 addend
 
 
 def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None,
@@ -394,7 +394,7 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
     if bias is not None:
         b32 = bias.to(device=x.device, dtype=torch.float32).contiguous()
     if M > _FOLD_MIN_ROWS:
-        # prefill: the zero-point term rides in the contraction as extra k-tiles, no [M, N] addend
+        # tensor-core kernels: the zero-point term rides in the contraction as extra k-tiles, no [M, N] addend
         rows = torch.empty((M, 64 * pre.fold_ktiles), dtype=torch.bfloat16, device=x.device)
         y = torch.empty((M, N), dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device):

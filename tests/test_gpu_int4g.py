@@ -258,14 +258,17 @@ def test_addend_many_rows_and_ragged_tiles(mo, cuda_dev):
 
 
 @pytest.mark.parametrize("M,K,N,gs,xdtype,shift", [
+    (17, 256, 200, 128, torch.float16, 0.0),
+    (100, 8192, 520, 128, torch.bfloat16, 0.0),          # the small-batch kernel, clusters splitting the extended k range
+    (128, 2080, 520, 32, torch.float16, 0.08),
     (300, 256, 200, 128, torch.float16, 0.0),
     (129, 4096, 1000, 128, torch.bfloat16, 0.05),       # zero points far from 8: the term is 15 x the main product
     (513, 2080, 520, 32, torch.float16, 0.08),          # odd number of k-tiles, seven fold tiles
     (2048, 4096, 264, 128, torch.bfloat16, 0.0),
 ])
 def test_folded_zero_point_term_matches_the_addend_path(mo, cuda_dev, M, K, N, gs, xdtype, shift):
-    """Above 128 rows matmul_int4 carries the zero-point term inside the contraction (extra k-tiles, bf16
-    three-way splits).  It must agree with the fp32-addend path to a unit of the output type, and with
+    """Above 16 rows matmul_int4 carries the zero-point term inside the contraction (extra k-tiles, bf16
+    three-way splits; both tensor-core kernels).  It must agree with the fp32-addend path to a unit of the output type, and with
     the fp64 product of the dequantised weight like that path does; bias and activation included."""
     from metalops_b200 import quantization as Q
     g = torch.Generator().manual_seed(M + K)
