@@ -60,8 +60,9 @@ static_assert(SMEM_DYN <= 227 * 1024, "shared memory");
 __device__ int g_status = 0;
 
 // GENERAL: the epilogue adds the fp32 addend and applies the activation; without it (its own instantiation,
-// so that the common case keeps its registers) it only converts and stores.
-template <bool BF16, bool GENERAL>
+// so that the common case keeps its registers) it only converts and stores.  FOLD: the item's first KX
+// k-tiles are the group-wise format's folded zero-point term.
+template <bool BF16, bool GENERAL, bool FOLD>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_r,
                const uint8_t *__restrict__ prepacked, const uint16_t *__restrict__ corr_op, int KX, int M, int64_t K, int64_t N,
@@ -88,11 +89,11 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     const int panels = (NT + PANEL_TILES - 1) / PANEL_TILES;
     const int row_tiles = (M + rows - 1) / rows;               // `rows`: height of a row tile, chosen by the host
     const int items = panels * row_tiles;
-    // Folded rank-G term (GENERAL only): KX further k-tiles whose A operand is read as bf16 from corr_op
+    // Folded rank-G term (FOLD only): KX further k-tiles whose A operand is read as bf16 from corr_op
     // [N, 64 KX] and whose X slices come from a second tensor map (bf16 [M, 64 KX]); KT counts all k-tiles.
     // They come first in an item, so that their operand loads (global memory, not the ring) pass while the
     // previous item's accumulator is still being read out.
-    const int KF = GENERAL ? KX : 0;                                       // k-tiles of the folded term, first in every item
+    const int KF = FOLD ? KX : 0;                                       // k-tiles of the folded term, first in every item
     const int KT = KU + KF;
     const int spi = (KT + STAGE_STEPS - 1) / STAGE_STEPS;                  // stages per item
 
@@ -259,14 +260,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 #pragma unroll
                                 for (int j = 0; j < 16; ++j) a[j] = j < jn ? __ldg(addend + (size_t)(m0 + j) * ld_add + n) : 0.0f;
                             }
-                            if (act == 0) {                       // uniform: the activation switch once per chunk
+                            if (act == 0 && jn == 16) {           // uniform: a full chunk without activation
 #pragma unroll
                                 for (int j = 0; j < 16; ++j, yp += ldy) {
-                                    if (j < jn) {
-                                        const float f = __uint_as_float(v[u][j]) + a[j];          // fp32 term added before the one rounding
-                                        if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-                                        else *yp = __half_as_ushort(__float2half_rn(f));
-                                    }
+                                    const float f = __uint_as_float(v[u][j]) + a[j];              // fp32 term added before the one rounding
+                                    if constexpr (BF16) *yp = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                                    else *yp = __half_as_ushort(__float2half_rn(f));
                                 }
                             } else {
 #pragma unroll
@@ -315,7 +314,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 if (!mbar_wait_warp(bar_empty(s), ((gq / ST) & 1) ^ 1, abort_flag, &g_status, 608)) goto done;
                 tc_fence_after();
                 const uint32_t a_addr = lane_taddr + (uint32_t)(A_COL0 + (s * STAGE_STEPS + sub) * 32);
-                if (!GENERAL || i >= KF) {
+                if (!FOLD || i >= KF) {
                     dequant_tile_to_tmem<BF16>(base + SMEM_RING + wslot * W_STAGE_BYTES + sub * TILE_BYTES, woff, doff, a_addr);
                 } else {
                     // a k-tile of the folded term: this thread's column of corr_op, 64 bf16 = 2 x 16 words
@@ -364,7 +363,7 @@ done:
     }
 }
 
-template <bool BF16, bool GENERAL>
+template <bool BF16, bool GENERAL, bool FOLD>
 static int launch(const CUtensorMap &tmap, const CUtensorMap &tmap_r, const void *prepacked, const void *corr_op, int KX, int M,
                   int64_t K, int64_t N, void *y, int64_t ldy, const float *addend, int64_t ld_add, int rows, int act, int sms,
                   cudaStream_t st) {
@@ -375,13 +374,13 @@ static int launch(const CUtensorMap &tmap, const CUtensorMap &tmap_r, const void
         Q4B_CUDA_TRY(cudaGetDevice(&dev));
         std::lock_guard<std::mutex> attr_lock(attr_mu);
         if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_wt_kernel<BF16, GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+            Q4B_CUDA_TRY(cudaFuncSetAttribute(gemm_wt_kernel<BF16, GENERAL, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
     const int64_t items = ceil_div(tiles_n(N), PANEL_TILES) * ceil_div(M, rows);
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    gemm_wt_kernel<BF16, GENERAL><<<grid, THREADS, SMEM_DYN, st>>>(tmap, tmap_r, (const uint8_t *)prepacked, (const uint16_t *)corr_op, KX,
+    gemm_wt_kernel<BF16, GENERAL, FOLD><<<grid, THREADS, SMEM_DYN, st>>>(tmap, tmap_r, (const uint8_t *)prepacked, (const uint16_t *)corr_op, KX,
                                                                   M, K, N, (uint16_t *)y, ldy, addend, ld_add, rows, act);
     Q4B_LAUNCH_CHECK();
     return Q4B_OK;
@@ -412,11 +411,17 @@ int gemm_wt_launch(const void *x, int bf16, int M, int64_t ldx, const void *prep
         tmap_r = tmap;
     }
     const int act = act_of_flags(flags);
-    if (addend != nullptr || act != 0 || fold)
-        return bf16 ? gemmwt::launch<true, true>(tmap, tmap_r, prepacked, corr_op, fold ? KX : 0, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st)
-                    : gemmwt::launch<false, true>(tmap, tmap_r, prepacked, corr_op, fold ? KX : 0, M, K, N, y, ldy, addend, ld_add, rows, act, sms, st);
-    return bf16 ? gemmwt::launch<true, false>(tmap, tmap_r, prepacked, nullptr, 0, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st)
-                : gemmwt::launch<false, false>(tmap, tmap_r, prepacked, nullptr, 0, M, K, N, y, ldy, nullptr, 0, rows, 0, sms, st);
+    const bool general = addend != nullptr || act != 0;
+#define Q4B_WT_LAUNCH(BF, GEN, FO)                                                                                              \
+    gemmwt::launch<BF, GEN, FO>(tmap, tmap_r, prepacked, FO ? corr_op : nullptr, FO ? KX : 0, M, K, N, y, ldy, GEN ? addend : nullptr, \
+                                GEN ? ld_add : 0, rows, GEN ? act : 0, sms, st)
+    if (bf16) {
+        if (general) return fold ? Q4B_WT_LAUNCH(true, true, true) : Q4B_WT_LAUNCH(true, true, false);
+        return fold ? Q4B_WT_LAUNCH(true, false, true) : Q4B_WT_LAUNCH(true, false, false);
+    }
+    if (general) return fold ? Q4B_WT_LAUNCH(false, true, true) : Q4B_WT_LAUNCH(false, true, false);
+    return fold ? Q4B_WT_LAUNCH(false, false, true) : Q4B_WT_LAUNCH(false, false, false);
+#undef Q4B_WT_LAUNCH
 }
 
 // read and clear this file's wait status (host side; the caller has synchronised the stream)
