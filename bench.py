@@ -686,10 +686,9 @@ def bench_sweeps(dev, stream, lib, peaks):
 
 def bench_groupwise_int4(dev, stream, lib, peaks):
     """The group-wise asymmetric INT4 format (K=4096, N=14336, group 128, bf16 activations) through the
-    C ABI with every buffer allocated once, as matmul_int4 runs it: at M = 1 the zero-point term as an
-    fp32 addend (q4b_int4g_addend: group sums, then the rank-G product) followed by q4b_matmul_addend on the
-    streaming tiles; at M = 2048 the term folded into the contraction (q4b_int4g_fold_rows, then
-    q4b_int4g_gemm_fold).  Next to each the same product on the tiles alone.  Four weights rotate."""
+    C ABI with every buffer allocated once, as matmul_int4 runs it: at M = 1 the rows' group sums
+    (q4b_int4g_rowsums) and the decode kernel forming the zero-point term in its epilogue (q4b_int4g_gemv);
+    at M = 2048 the term folded into the contraction (q4b_int4g_fold_rows, then q4b_int4g_gemm_fold).  Next to each the same product on the tiles alone.  Four weights rotate."""
     import metalops_b200 as mo
     from metalops_b200 import _cabi
     from metalops_b200 import quantization as Q
@@ -700,27 +699,25 @@ def bench_groupwise_int4(dev, stream, lib, peaks):
         w = (torch.randn(K, N, generator=g, device=dev) * 0.02).half()
         sets.append(Q.prepack_int4(*mo.quantize_int4(w, G), G))
         del w
-    out = {"config": f"K={K} N={N} group {G}, bf16 activations; M=1: fp32 [M, N] addend, M=2048: term folded into the contraction"}
+    out = {"config": f"K={K} N={N} group {G}, bf16 activations; M=1: term formed in the decode kernel's epilogue, M=2048: folded into the contraction"}
     for M in (1, 2048):
         x = torch.randn(M, K, generator=g, device=dev).bfloat16()
         y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-        adds = [torch.empty((M, N), dtype=torch.float32, device=dev) for _ in sets]
         rs = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, G) // 4, dtype=torch.float32, device=dev)
 
         rows = torch.empty((M, 64 * sets[0].fold_ktiles), dtype=torch.bfloat16, device=dev)
 
-        def full(i, M=M, x=x, y=y, adds=adds, rs=rs, rows=rows):
+        def full(i, M=M, x=x, y=y, rs=rs, rows=rows):
             sp = torch.cuda.current_stream(dev).cuda_stream
             p = sets[i % 4]
             if M > 16:         # tensor-core kernels: the zero-point term folded into the contraction (what matmul_int4 does)
                 rc = lib.q4b_int4g_fold_rows(x.data_ptr(), _cabi.BF16, M, K, K, G, rows.data_ptr(), sp)
                 rc = rc or lib.q4b_int4g_gemm_fold(x.data_ptr(), _cabi.BF16, M, K, p.tiles.data.data_ptr(), K, N, p.fold.data_ptr(),
                                                    rows.data_ptr(), p.fold_ktiles, None, y.data_ptr(), N, 0, sp)
-            else:
-                rc = lib.q4b_int4g_addend(x.data_ptr(), _cabi.BF16, M, K, p.corr.data_ptr(), None, K, N, G, rs.data_ptr(),
-                                          adds[i % 4].data_ptr(), sp)
-                rc = rc or lib.q4b_matmul_addend(x.data_ptr(), _cabi.BF16, M, K, p.tiles.data.data_ptr(), K, N, adds[i % 4].data_ptr(), N,
-                                                 y.data_ptr(), N, 0, sp)
+            else:              # decode kernels: the rows' group sums, the term formed in the product's epilogue
+                rc = lib.q4b_int4g_rowsums(x.data_ptr(), _cabi.BF16, M, K, K, G, rs.data_ptr(), sp)
+                rc = rc or lib.q4b_int4g_gemv(x.data_ptr(), _cabi.BF16, M, K, p.tiles.data.data_ptr(), K, N, p.corr.data_ptr(), rs.data_ptr(),
+                                              G, None, y.data_ptr(), N, 0, sp)
             if rc:
                 _cabi.check(rc, "group-wise INT4 matmul")
 

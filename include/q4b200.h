@@ -214,6 +214,16 @@ Q4B_API int q4b_int4g_fold_rows(const void *x, int x_dtype, int64_t M, int64_t l
 Q4B_API int q4b_int4g_gemm_fold(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
                                 int64_t K, int64_t N, const void *fold_operand, const void *fold_rows, int KX,
                                 const float *bias, void *y, int64_t ldy, int flags, void *stream);
+/*
+ * Up to 16 rows (the decode kernels): q4b_int4g_rowsums writes the rows' group sums [M, ceil(K/group)] fp32
+ * (q4b_int4g_rowsums_bytes), and q4b_int4g_gemv forms sum_g corr[g, n] * rowsums[m, g] in its epilogue,
+ * in fp32, before the one rounding; bias is one fp32 row of N values or NULL.
+ */
+Q4B_API int q4b_int4g_rowsums(const void *x, int x_dtype, int64_t M, int64_t ldx, int64_t K, int64_t group,
+                              float *rowsums_out, void *stream);
+Q4B_API int q4b_int4g_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                           int64_t N, const float *corr, const float *rowsums, int64_t group, const float *bias,
+                           void *y, int64_t ldy, int flags, void *stream);
 Q4B_API int q4b_int4g_matmul_generic(const void *x, int x_dtype, int64_t M, int64_t ldx,
                                      const void *packed, const void *scales, const void *zeros,
                                      int sz_dtype, int64_t K, int64_t N, int64_t group, void *y,

@@ -72,6 +72,8 @@ SYMBOLS = {
     "q4b_int4g_dequantize": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _ci, _vp]),
     "q4b_int4g_prepack": (_ci, [_vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _vp, _vp]),
     "q4b_int4g_rowsums_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
+    "q4b_int4g_rowsums": (_ci, [_vp, _ci, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "q4b_int4g_gemv": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _ci, _vp]),
     "q4b_int4g_fold_ktiles": (_ci, [_i64, _i64]),
     "q4b_int4g_fold_operand": (_ci, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "q4b_int4g_fold_rows": (_ci, [_vp, _ci, _i64, _i64, _i64, _i64, _vp, _vp]),

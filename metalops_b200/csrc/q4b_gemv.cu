@@ -34,10 +34,15 @@ __device__ int g_wait_status = 0;                  // first bounded wait of this
 // Optional fused all-gather: when `world` > 0 the epilogue stores the result, instead of into y, at
 // column offset col0 of the [M, ld]-shaped output of EVERY rank (peer-mapped pointers; plain
 // stores over NVLink), so the column-parallel shards land gathered without a collective.
+// Optional rank-G term of the group-wise INT4 format: when corr is not null the epilogue adds
+// sum_g corr[g, n] * rowsums[m, g] (fp32; corr [G, N], rowsums [M, G]) before the one rounding, so that
+// no [M, N] addend has to exist.
 struct PeerOut {
     uint16_t *p[8];
     int world;
     int64_t col0, ld;
+    const float *corr, *rowsums;
+    int G;
 };
 
 
@@ -353,6 +358,11 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
 #pragma unroll
             for (int j = 0; j < KS; ++j) s += red[tl * KS + j][f][m8 * TILE_N + nl];
             if (addend != nullptr) s += addend[(size_t)m * ld_add + n];     // fp32 term added before the one rounding
+            if (peers.corr != nullptr) {                                    // consecutive threads: consecutive n
+                float t = 0.0f;
+                for (int gi = 0; gi < peers.G; ++gi) t = fmaf(__ldg(peers.corr + (size_t)gi * N + n), __ldg(peers.rowsums + (size_t)m * peers.G + gi), t);
+                s += t;
+            }
             s = apply_act(s, act);
             const uint16_t bits = out_bits<BF16>(s);
             if constexpr (!GATHER) {
@@ -577,6 +587,11 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
 #pragma unroll
             for (int j = 0; j < KS; ++j) sum += red[tl * KS + j][nl];
             if (addend != nullptr) sum += addend[n];           // fp32 term added before the one rounding
+            if (peers.corr != nullptr) {                       // consecutive threads: consecutive n
+                float t = 0.0f;
+                for (int gi = 0; gi < peers.G; ++gi) t = fmaf(__ldg(peers.corr + (size_t)gi * N + n), __ldg(peers.rowsums + gi), t);
+                sum += t;
+            }
             const uint16_t bits = out_bits<BF16>(apply_act(sum, act));
             if constexpr (!GATHER) {
                 y[n] = bits;
@@ -737,6 +752,21 @@ extern "C" int q4b_gemv_addend(const void *x, int x_dtype, int64_t M, int64_t ld
                                int64_t N, const float *addend, int64_t ld_add, void *y, int64_t ldy, int flags,
                                void *stream) {
     return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, addend, ld_add, y, ldy, flags, stream, PeerOut{});
+}
+
+// The group-wise INT4 product for up to 16 rows with its zero-point term formed in the epilogue from the
+// rows' group sums (rowsums [M, G] fp32, from q4b_int4g_rowsums) and corr [G, N]; bias: one fp32 row or NULL.
+extern "C" int q4b_int4g_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                              const float *corr, const float *rowsums, int64_t group, const float *bias, void *y, int64_t ldy,
+                              int flags, void *stream) {
+    if (corr == nullptr || rowsums == nullptr || group < 1 || K < 1) return Q4B_ERR_ARG;
+    const int64_t G = ceil_div(K, group);
+    if (G > 65535) return Q4B_ERR_SHAPE;
+    PeerOut po = {};
+    po.corr = corr;
+    po.rowsums = rowsums;
+    po.G = (int)G;
+    return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, bias, 0, y, ldy, flags, stream, po);
 }
 
 extern "C" int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,

@@ -465,6 +465,23 @@ extern "C" size_t q4b_int4g_rowsums_bytes(int64_t M, int64_t K, int64_t group) {
     return (size_t)M * (size_t)ceil_div(K, group) * sizeof(float);
 }
 
+extern "C" int q4b_int4g_rowsums(const void *x, int x_dtype, int64_t M, int64_t ldx, int64_t K, int64_t group, float *rowsums_out,
+                                 void *stream) {
+    if (x == nullptr || rowsums_out == nullptr) return Q4B_ERR_ARG;
+    if (M < 1 || ldx < K || K < 1 || group < 1) return Q4B_ERR_ARG;
+    const int64_t G = ceil_div(K, group);
+    const int64_t pairs = M * G;
+    const unsigned grid1 = (unsigned)(ceil_div(pairs, 8) < 16384 ? ceil_div(pairs, 8) : 16384);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case Q4B_F16: int4g_rowsum_kernel<__half><<<grid1, 256, 0, st>>>((const __half *)x, M, ldx, K, group, (int)G, rowsums_out); break;
+        case Q4B_BF16: int4g_rowsum_kernel<__nv_bfloat16><<<grid1, 256, 0, st>>>((const __nv_bfloat16 *)x, M, ldx, K, group, (int)G, rowsums_out); break;
+        default: return Q4B_ERR_DTYPE;
+    }
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
 extern "C" int q4b_int4g_addend(const void *x, int x_dtype, int64_t M, int64_t ldx, const float *corr, const float *bias,
                                 int64_t K, int64_t N, int64_t group, float *rowsums_ws, float *addend_out, void *stream) {
     if (x == nullptr || corr == nullptr || addend_out == nullptr || rowsums_ws == nullptr) return Q4B_ERR_ARG;

@@ -375,7 +375,8 @@ def prepack_int4(W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
 
 
 _ACT_FLAGS = {None: 0, "none": 0, "silu": _cabi.FLAG_ACT_SILU, "gelu": _cabi.FLAG_ACT_GELU}
-_FOLD_MIN_ROWS = 16         # above: the tensor-core kernels with the zero-point term folded in; up to it: the fp32 addend
+_FOLD_MIN_ROWS = 16         # above: the tensor-core kernels with the zero-point term folded into the contraction;
+                            # up to it: the decode kernels, which form the term in their epilogue
 
 
 def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None,
@@ -393,7 +394,8 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
     b32 = None
     if bias is not None:
         b32 = bias.to(device=x.device, dtype=torch.float32).contiguous()
-    if M > _FOLD_MIN_ROWS:
+    # the same split between the decode and the tensor-core kernels as q4b_matmul makes
+    if M > _FOLD_MIN_ROWS or (M > 8 and K * N >= (1 << 25)):
         # tensor-core kernels: the zero-point term rides in the contraction as extra k-tiles, no [M, N] addend
         rows = torch.empty((M, 64 * pre.fold_ktiles), dtype=torch.bfloat16, device=x.device)
         y = torch.empty((M, N), dtype=x.dtype, device=x.device)
@@ -407,15 +409,35 @@ def _matmul_int4_prepacked(X2: torch.Tensor, pre: Int4GPrepacked, bias: Optional
                                          _ACT_FLAGS[activation], sp)
         _cabi.check(rc, "matmul_int4")
         return y.float() if in_dtype == torch.float32 else y
+    # decode kernels (up to 16 rows): the rows' group sums, then the product with the term formed in its epilogue
+    rowsums = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, pre.group_size) // 4, dtype=torch.float32, device=x.device)
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        sp = _cabi.stream_ptr(x.device)
+        rc = lib.q4b_int4g_rowsums(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), K, pre.group_size, rowsums.data_ptr(), sp)
+        _cabi.check(rc, "matmul_int4")
+        rc = lib.q4b_int4g_gemv(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.tiles.data.data_ptr(), K, N,
+                                pre.corr.data_ptr(), rowsums.data_ptr(), pre.group_size,
+                                b32.data_ptr() if b32 is not None else None, y.data_ptr(), y.stride(0), _ACT_FLAGS[activation], sp)
+    _cabi.check(rc, "matmul_int4")
+    return y.float() if in_dtype == torch.float32 else y
+
+
+def _matmul_int4_via_addend(x: torch.Tensor, pre: Int4GPrepacked, bias: Optional[torch.Tensor] = None,
+                            activation: Optional[str] = None) -> torch.Tensor:
+    """The same product with the zero-point term as an explicit fp32 ``[M, N]`` addend
+    (``q4b_int4g_addend`` + ``q4b_matmul_addend``): the form every kernel accepts, kept for comparison."""
+    M, K, N = x.shape[0], pre.tiles.K, pre.tiles.N
+    lib = _cabi.load()
     addend = torch.empty((M, N), dtype=torch.float32, device=x.device)
     rowsums = torch.empty(lib.q4b_int4g_rowsums_bytes(M, K, pre.group_size) // 4, dtype=torch.float32, device=x.device)
+    b32 = bias.to(device=x.device, dtype=torch.float32).contiguous() if bias is not None else None
     with torch.cuda.device(x.device):
         rc = lib.q4b_int4g_addend(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], M, x.stride(0), pre.corr.data_ptr(),
                                   b32.data_ptr() if b32 is not None else None, K, N, pre.group_size,
                                   rowsums.data_ptr(), addend.data_ptr(), _cabi.stream_ptr(x.device))
     _cabi.check(rc, "matmul_int4")
-    y = _matmul_prepacked(x, pre.tiles, addend=addend, flags=_ACT_FLAGS[activation])
-    return y.float() if in_dtype == torch.float32 else y
+    return _matmul_prepacked(x, pre.tiles, addend=addend, flags=_ACT_FLAGS[activation])
 
 
 def matmul_int4(X: torch.Tensor, W_packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,

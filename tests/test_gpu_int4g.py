@@ -258,6 +258,9 @@ def test_addend_many_rows_and_ragged_tiles(mo, cuda_dev):
 
 
 @pytest.mark.parametrize("M,K,N,gs,xdtype,shift", [
+    (1, 4096, 1000, 128, torch.float16, 0.05),           # the decode kernels: the term formed in the epilogue
+    (7, 2080, 520, 32, torch.bfloat16, 0.08),
+    (16, 256, 200, 128, torch.float16, 0.0),
     (17, 256, 200, 128, torch.float16, 0.0),
     (100, 8192, 520, 128, torch.bfloat16, 0.0),          # the small-batch kernel, clusters splitting the extended k range
     (128, 2080, 520, 32, torch.float16, 0.08),
@@ -268,7 +271,7 @@ def test_addend_many_rows_and_ragged_tiles(mo, cuda_dev):
 ])
 def test_folded_zero_point_term_matches_the_addend_path(mo, cuda_dev, M, K, N, gs, xdtype, shift):
     """Above 16 rows matmul_int4 carries the zero-point term inside the contraction (extra k-tiles, bf16
-    three-way splits; both tensor-core kernels).  It must agree with the fp32-addend path to a unit of the output type, and with
+    three-way splits; both tensor-core kernels); up to 16 rows the decode kernels form it in their epilogue.  It must agree with the fp32-addend path to a unit of the output type, and with
     the fp64 product of the dequantised weight like that path does; bias and activation included."""
     from metalops_b200 import quantization as Q
     g = torch.Generator().manual_seed(M + K)
@@ -282,13 +285,8 @@ def test_folded_zero_point_term_matches_the_addend_path(mo, cuda_dev, M, K, N, g
     y_fold = Q._matmul_int4_prepacked(x, pre)
     yb_fold = Q._matmul_int4_prepacked(x, pre, bias=bias, activation="silu")
     assert Q.wait_status(cuda_dev) == 0
-    keep = Q._FOLD_MIN_ROWS
-    try:
-        Q._FOLD_MIN_ROWS = 1 << 30
-        y_add = Q._matmul_int4_prepacked(x, pre)
-        yb_add = Q._matmul_int4_prepacked(x, pre, bias=bias, activation="silu")
-    finally:
-        Q._FOLD_MIN_ROWS = keep
+    y_add = Q._matmul_int4_via_addend(x, pre)
+    yb_add = Q._matmul_int4_via_addend(x, pre, bias=bias, activation="silu")
     e_fold, e_add = orc.rel_l2(y_fold, ref.float()), orc.rel_l2(y_add, ref.float())
     assert e_fold <= max(1.05 * e_add, 1e-4), (e_fold, e_add)
     ulp = 2.0 ** (-7 if xdtype == torch.bfloat16 else -10)
