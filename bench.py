@@ -867,7 +867,7 @@ def run_probe(spec: str) -> None:
     """`--probe MxKxN`: six distinct weights, a warm-up launch and then one q4b_matmul launch each (fp16 activations), then the
     wait status; prints the average device time.  `--probe chain:L`: L layers of the 7B-shaped stage
     list, three runs.  `--probe quantize:NxK`: the packer on three fp16 [N, K] weights, both output
-    forms.  Small fixed cases for profiler captures."""
+    forms.  `--probe int4g:M`: matmul_int4 (K=4096, N=14336, group 128, bf16) three times.  Small fixed cases for profiler captures."""
     from metalops_b200 import _cabi
     from metalops_b200 import quantization as Q
     dev = torch.device("cuda", 0)
@@ -887,6 +887,24 @@ def run_probe(spec: str) -> None:
         torch.cuda.synchronize(dev)
         print(json.dumps({"probe": spec, "launches": 3, "us_per_launch": e0.elapsed_time(e1) * 1e3 / 3,
                           "bytes_per_launch": sum(gemv_bytes(1, K, N) for _, K, N, _ in stack), "wait_status": Q.wait_status(dev)}))
+        return
+    if spec.startswith("int4g:"):
+        import metalops_b200 as mo
+        M = int(spec.split(":")[1])
+        K, N, G = 4096, 14336, 128
+        g = torch.Generator(device=dev).manual_seed(4242)
+        w = (torch.randn(K, N, generator=g, device=dev) * 0.02).half()
+        p, s_, z = mo.quantize_int4(w, G)
+        x = torch.randn(M, K, generator=g, device=dev).bfloat16()
+        y = mo.matmul_int4(x, p, s_, z, G)                         # prepacks once, warms up
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            y = mo.matmul_int4(x, p, s_, z, G)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        print(json.dumps({"probe": spec, "launches": 3, "us_per_product": e0.elapsed_time(e1) * 1e3 / 3, "wait_status": Q.wait_status(dev)}))
         return
     if spec.startswith("quantize:"):
         N, K = (int(v) for v in spec.split(":")[1].lower().split("x"))
@@ -930,7 +948,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--probe", default=None, metavar="MxKxN|chain:L|quantize:NxK", help="run one small case and exit (profiler captures)")
+    ap.add_argument("--probe", default=None, metavar="MxKxN|chain:L|quantize:NxK|int4g:M", help="run one small case and exit (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-gemm", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
