@@ -853,13 +853,31 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
                 if world > 1:
                     dist.barrier()
                     e["nccl_all_reduce_fp32"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, with_reduce, reps, graph=False)))
+                    if M == 1:
+                        try:
+                            ex = S._PeerExchange(16, world * N, dev)
+                            out = torch.empty(M, N, device=dev, dtype=torch.float16)
+
+                            def fused_reduce(i, x=x, ex=ex, out=out):
+                                p = pres[i % len(pres)]
+                                ptrs, local_ll, epoch = ex.next()
+                                rc = lib.q4b_gemv_exchange(x.data_ptr(), _cabi.F16, 1, k_loc, p.data.data_ptr(), k_loc, N, ptrs, world,
+                                                           rank * N, world * N, local_ll, world, epoch, out.data_ptr(), N, 0,
+                                                           torch.cuda.current_stream(dev).cuda_stream)
+                                if rc:
+                                    _cabi.check(rc, "q4b_gemv_exchange")
+                            dist.barrier()
+                            e["fused_peer_store_reduce"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, fused_reduce, reps, graph=False)))
+                        except Exception as ex_:          # symmetric memory unavailable on this box
+                            e["fused_peer_store_reduce"] = {"error": str(ex_)[:200]}
                 entry[f"row_parallel_m{M}"] = e
             del pres
             torch.cuda.empty_cache()
         res[label] = entry
     if world > 1:
         res["limit"] = ("at M = 1 a rank's product takes a few microseconds, so the step is bounded by the collective's latency "
-                        "(NCCL launch + ring/tree steps, or two symmetric-memory barriers for the fused form), not by HBM")
+                        "(NCCL launch + ring/tree steps; for the fused forms a peer store over NVLink and the readers' polling, "
+                        "no barrier), not by HBM")
     return res
 
 

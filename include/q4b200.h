@@ -322,6 +322,26 @@ Q4B_API int q4b_chain_run(const void *workspace, int n_stages, int x_dtype, int6
 Q4B_API int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ldx,
                             const void *prepacked, int64_t K, int64_t N, void *const *y_ranks,
                             int world, int64_t col0, int64_t ld_out, int flags, void *stream);
+/*
+ * The same gather without barriers: the peers' buffers are uint32 [rows, ld_out] and every store carries
+ * the call's epoch (1..65535) in its upper half, so each word validates itself.  q4b_gather_ll_unpack, on
+ * every rank, waits word by word (bounded; q4b_wait_status code 700) for the epoch and writes the plain
+ * values; with slots > 1 it adds the `slots` partial results that sit side by side in a row (fp32, slot
+ * order, one rounding): the reduction of a row-parallel layer.  Alternate between two buffers from call
+ * to call: stream order then guarantees that nobody still reads the buffer being overwritten.
+ */
+Q4B_API int q4b_gemv_gather_ll(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+                               int64_t K, int64_t N, void *const *ll_ranks, int world, int64_t col0,
+                               int64_t ld_out, int epoch, int flags, void *stream);
+Q4B_API int q4b_gather_ll_unpack(const void *ll, int64_t rows, int64_t cols, int64_t ld_ll, int slots, int epoch,
+                                 int x_dtype, void *out, int64_t ld_out, void *stream);
+/* both steps in one call: the product stored into every rank's words, then this rank's wait-and-unpack of
+ * its own buffer ll_local into out (slots == 1: gather, out [M, ld_out]; slots > 1: sum of the partial
+ * results, ld_out = slots * N, out [M, N]) */
+Q4B_API int q4b_gemv_exchange(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                              int64_t N, void *const *ll_ranks, int world, int64_t col0, int64_t ld_out,
+                              const void *ll_local, int slots, int epoch, void *out, int64_t ld_y, int flags,
+                              void *stream);
 
 /*
  * RMSNorm in front of a quantised linear layer, the first step of the reference's
@@ -338,7 +358,7 @@ Q4B_API int q4b_rmsnorm(const void *x, int dtype, int64_t M, int64_t K, int64_t 
  * synchronises the stream, reads that word and clears it: Q4B_OK, or Q4B_ERR_TIMEOUT with
  * *detail (may be NULL) = which wait gave up (100-101 decode kernels, 401-407 small-batch
  * tensor-memory kernel, 500-504 persistent single-row kernel, 601-608 persistent prefill kernel,
- * 900 self-test).
+ * 700 barrier-free gather, 900 self-test).
  * It never traps or faults the device.
  */
 Q4B_API int q4b_wait_status(void *stream, int *detail);

@@ -54,6 +54,10 @@ SYMBOLS = {
     "q4b_wait_status": (_ci, [_vp, ctypes.POINTER(_ci)]),
     "q4b_selftest_wait_timeout": (_ci, [_i64, _vp]),
     "q4b_gemv_gather": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _vp]),
+    "q4b_gemv_gather_ll": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _ci, _vp]),
+    "q4b_gather_ll_unpack": (_ci, [_vp, _i64, _i64, _i64, _ci, _ci, _ci, _vp, _i64, _vp]),
+    "q4b_gemv_exchange": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _vp, _ci, _ci, _vp, _i64,
+                                _ci, _vp]),
     "q4b_import_ggml": (_ci, [_vp, _i64, _i64, _vp, _vp]),
     "q4b_quantize_ggml": (_ci, [_vp, _ci, _i64, _i64, _ci, _vp, _vp, _vp]),
     "q4b_int8g_matmul": (_ci, [_vp, _ci, _i64, _i64, _vp, _vp, _vp, _ci, _i64, _i64, _i64, _vp, _i64, _vp]),

@@ -43,6 +43,9 @@ struct PeerOut {
     int64_t col0, ld;
     const float *corr, *rowsums;
     int G;
+    // ll_tag != 0: the peers' buffers hold 32-bit words and each store is (value | ll_tag), the tag being
+    // the call's epoch in the upper half: a word validates itself, so the reader needs no barrier.
+    uint32_t ll_tag;
 };
 
 
@@ -370,7 +373,11 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
             } else {
 #pragma unroll
                 for (int r = 0; r < 8; ++r)        // static indices: the pointers stay in the parameter bank
-                    if (r < peers.world) peers.p[r][(size_t)m * peers.ld + peers.col0 + n] = bits;
+                    if (r < peers.world) {
+                        const size_t at = (size_t)m * peers.ld + peers.col0 + n;
+                        if (peers.ll_tag != 0) reinterpret_cast<uint32_t *>(peers.p[r])[at] = (uint32_t)bits | peers.ll_tag;
+                        else peers.p[r][at] = bits;
+                    }
             }
         }
     }
@@ -598,7 +605,10 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
             } else {
 #pragma unroll
                 for (int r = 0; r < 8; ++r)        // static indices: the pointers stay in the parameter bank
-                    if (r < peers.world) peers.p[r][peers.col0 + n] = bits;
+                    if (r < peers.world) {
+                        if (peers.ll_tag != 0) reinterpret_cast<uint32_t *>(peers.p[r])[peers.col0 + n] = (uint32_t)bits | peers.ll_tag;
+                        else peers.p[r][peers.col0 + n] = bits;
+                    }
             }
         }
     }
@@ -705,6 +715,44 @@ static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const v
 }
 
 
+// Reader side of the self-validating words: every thread polls its words until they carry this call's tag
+// (bounded: code 700 and zeros on giving up), then writes the plain values.  SLOTS > 1: the row holds SLOTS
+// partial results side by side (one per rank), summed here in fp32 in slot order and rounded once.
+constexpr long long LL_WAIT_CYCLES = 1LL << 29;      // ~0.3 s
+template <bool BF16, bool SUM>
+__global__ void __launch_bounds__(256)
+ll_unpack_kernel(const uint32_t *ll, int rows, int64_t cols, int64_t ld_ll, int slots, uint32_t tag, uint16_t *__restrict__ out,
+                 int64_t ld_out) {
+    const int64_t total = (int64_t)rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int64_t m = i / cols, n = i % cols;
+        float acc = 0.0f;
+        uint32_t last = 0;
+        for (int sl = 0; sl < slots; ++sl) {
+            const uint32_t *w = ll + m * ld_ll + (int64_t)sl * cols + n;
+            uint32_t v;
+            long long t0 = 0;
+            for (int it = 0;; ++it) {
+                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
+                if ((v & 0xFFFF0000u) == tag) break;
+                if ((it & 15) == 15) {
+                    const long long now = clock64();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > LL_WAIT_CYCLES) {
+                        atomicCAS(&g_wait_status, 0, 700);
+                        v = 0;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            last = v & 0xFFFFu;
+            if (SUM) acc += BF16 ? __bfloat162float(__ushort_as_bfloat16((uint16_t)last)) : __half2float(__ushort_as_half((uint16_t)last));
+        }
+        out[m * ld_out + n] = SUM ? out_bits<BF16>(acc) : (uint16_t)last;
+    }
+}
+
 // read and clear this file's wait status (host side; the caller has synchronised the stream)
 int gemv_wait_status(int *value) {
     int h = 0;
@@ -767,6 +815,59 @@ extern "C" int q4b_int4g_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx
     po.rowsums = rowsums;
     po.G = (int)G;
     return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, bias, 0, y, ldy, flags, stream, po);
+}
+
+// The gather without barriers: the peers' buffers are uint32 [rows, ld_out] and every store carries the call's
+// epoch (1..65535) in its upper half; q4b_gather_ll_unpack on each rank waits, word by word and bounded, for
+// all words of the epoch and writes the plain result.  The caller alternates between two buffers from call
+// to call (stream order then guarantees that nobody still reads the buffer being overwritten).
+extern "C" int q4b_gemv_gather_ll(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,
+                                  int64_t N, void *const *ll_ranks, int world, int64_t col0, int64_t ld_out, int epoch, int flags,
+                                  void *stream) {
+    if (ll_ranks == nullptr || world < 1 || world > 8 || col0 < 0 || ld_out < col0 + N) return Q4B_ERR_ARG;
+    if (epoch < 1 || epoch > 65535) return Q4B_ERR_ARG;
+    for (int r = 0; r < world; ++r)
+        if (ll_ranks[r] == nullptr || !aligned(ll_ranks[r], 4)) return Q4B_ERR_ARG;
+    PeerOut po = {};
+    for (int r = 0; r < world; ++r) po.p[r] = (uint16_t *)ll_ranks[r];
+    po.world = world;
+    po.col0 = col0;
+    po.ld = ld_out;
+    po.ll_tag = (uint32_t)epoch << 16;
+    return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, ll_ranks[0], ld_out, flags, stream, po);
+}
+
+// slots == 1: out[m, n] = value of ll[m, n].  slots > 1: out[m, n] = sum over s of ll[m, s * cols + n], fp32, slot
+// order, one rounding to x_dtype (the partial products of a row-parallel layer).
+extern "C" int q4b_gather_ll_unpack(const void *ll, int64_t rows, int64_t cols, int64_t ld_ll, int slots, int epoch, int x_dtype,
+                                    void *out, int64_t ld_out, void *stream) {
+    if (ll == nullptr || out == nullptr || rows < 1 || rows > 16 || cols < 1 || slots < 1 || slots > 8) return Q4B_ERR_ARG;
+    if (ld_ll < (int64_t)slots * cols || ld_out < cols || epoch < 1 || epoch > 65535) return Q4B_ERR_ARG;
+    if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
+    const int64_t total = rows * cols;
+    const unsigned grid = (unsigned)(ceil_div(total, 256) < 1184 ? ceil_div(total, 256) : 1184);
+    const uint32_t tag = (uint32_t)epoch << 16;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (slots == 1)
+        ll_unpack_kernel<false, false><<<grid, 256, 0, st>>>((const uint32_t *)ll, (int)rows, cols, ld_ll, 1, tag, (uint16_t *)out, ld_out);
+    else if (x_dtype == Q4B_BF16)
+        ll_unpack_kernel<true, true><<<grid, 256, 0, st>>>((const uint32_t *)ll, (int)rows, cols, ld_ll, slots, tag, (uint16_t *)out, ld_out);
+    else
+        ll_unpack_kernel<false, true><<<grid, 256, 0, st>>>((const uint32_t *)ll, (int)rows, cols, ld_ll, slots, tag, (uint16_t *)out, ld_out);
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
+// Both steps of the barrier-free exchange in one call: the product stored into every rank's words, then the
+// wait-and-unpack of this rank's own words (ll_local = this rank's entry of ll_ranks) into out.
+// slots == 1: a gather (out is [M, ld_out] wide, col0 = this rank's first column); slots > 1: the reduction of
+// `slots` partial results (ld_out = slots * N, col0 = rank * N; out is [M, N]).
+extern "C" int q4b_gemv_exchange(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                                 void *const *ll_ranks, int world, int64_t col0, int64_t ld_out, const void *ll_local, int slots,
+                                 int epoch, void *out, int64_t ld_y, int flags, void *stream) {
+    if (int rc = q4b_gemv_gather_ll(x, x_dtype, M, ldx, prepacked, K, N, ll_ranks, world, col0, ld_out, epoch, flags, stream)) return rc;
+    const int64_t cols = slots > 1 ? N : ld_out;
+    return q4b_gather_ll_unpack(ll_local, M, cols, ld_out, slots, epoch, x_dtype, out, ld_y, stream);
 }
 
 extern "C" int q4b_gemv_gather(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K,

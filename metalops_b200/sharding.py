@@ -45,6 +45,37 @@ def gather_columns(y_local: torch.Tensor, group=None, world: Optional[int] = Non
     return buf.view(world, M, n_local).permute(1, 0, 2).reshape(M, world * n_local)
 
 
+class _PeerExchange:
+    """Two ``[max_rows, width]`` uint32 buffers in symmetric memory (peer-mapped on every rank) and the epoch
+    counter of the barrier-free exchange: a decode kernel stores (value | epoch << 16) into every rank's
+    buffer (q4b_gemv_gather_ll), and each rank's q4b_gather_ll_unpack waits, word by word and bounded, for
+    the epoch.  Calls alternate between the two buffers, so with every rank running its calls in stream
+    order nobody can still be reading the buffer that a peer overwrites.  The one barrier is at set-up."""
+
+    def __init__(self, max_rows: int, width: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.max_rows, self.width = max_rows, width
+        self.buf = symm_mem.empty((2, max_rows, width), dtype=torch.int32, device=device)
+        self.buf.zero_()                                     # epoch 0 is never used
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        torch.cuda.synchronize(device)
+        self.hdl.barrier()                                   # every rank's buffers are cleared before anyone stores
+        half = max_rows * width * 4
+        import ctypes
+        self.ptrs = [(ctypes.c_void_p * len(self.hdl.buffer_ptrs))(*[int(p) + par * half for p in self.hdl.buffer_ptrs])
+                     for par in (0, 1)]
+        self.local = [self.buf[0].data_ptr(), self.buf[1].data_ptr()]
+        self.calls = 0
+
+    def next(self):
+        """(peer pointers of this call's buffer, address of this rank's own, epoch)"""
+        par = self.calls & 1
+        epoch = self.calls % 65535 + 1
+        self.calls += 1
+        return self.ptrs[par], self.local[par], epoch
+
+
 class ColumnParallelQ4Linear(nn.Module):
     """One rank's slice of a q4_0 linear layer, column-parallel over N.
 
@@ -80,74 +111,47 @@ class ColumnParallelQ4Linear(nn.Module):
 
     # ---- fused all-gather for decode (M <= 16): the kernel's epilogue stores into every rank's output ----
     def enable_fused_gather(self, max_rows: int = 16, dtype: torch.dtype = torch.float16) -> None:
-        """Allocate the gathered output ``[max_rows, N]`` in symmetric memory (peer-mapped on every
+        """Allocate the exchange buffers ``2 x [max_rows, N]`` in symmetric memory (peer-mapped on every
         rank of the group) once.  Needs equal shards (N divisible by the world size) and CUDA."""
-        import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm_mem
         if self.N % self.world:
             raise RuntimeError("fused gather needs N divisible by the number of ranks")
-        dev = self.weight_blocks.device
-        group = self.group if self.group is not None else dist.group.WORLD
-        self._gather_buf = symm_mem.empty((max_rows, self.N), dtype=dtype, device=dev)
-        self._gather_hdl = symm_mem.rendezvous(self._gather_buf, group)
-        self._gather_ptrs = [int(p) for p in self._gather_hdl.buffer_ptrs]
+        self._gather = FusedGatherBuffer(self.N, self.rank, self.world, dtype, self.weight_blocks.device, self.group, max_rows)
 
     def forward_fused_gather(self, x: torch.Tensor) -> torch.Tensor:
         """``[M, N]`` on every rank, M <= 16: each rank's decode kernel writes its columns into all
-        ranks' outputs over NVLink; a symmetric-memory barrier on the stream orders the reads.  The
-        returned tensor is a view of the shared buffer, valid until the next call."""
-        import ctypes
-        from . import _cabi
-        if getattr(self, "_gather_hdl", None) is None:
+        ranks' buffers over NVLink as self-validating words; no barrier, no collective."""
+        if getattr(self, "_gather", None) is None:
             raise RuntimeError("call enable_fused_gather() first")
-        M = x.shape[0]
-        if M > self._gather_buf.shape[0] or M > 16 or x.dtype != self._gather_buf.dtype:
-            raise RuntimeError("fused gather serves up to 16 rows of the dtype it was enabled for")
-        pre = Q.prepack_ggml_q4_0(self.weight_blocks)
-        xc = x.contiguous()
-        self._gather_hdl.barrier()                      # nobody still reads the previous result
-        ptrs = (ctypes.c_void_p * self.world)(*self._gather_ptrs)
-        with torch.cuda.device(xc.device):
-            rc = _cabi.load().q4b_gemv_gather(xc.data_ptr(), _cabi.DTYPE_CODE[xc.dtype], M, xc.stride(0), pre.data.data_ptr(),
-                                              pre.K, pre.N, ptrs, self.world, self.n0, self.N, 0, _cabi.stream_ptr(xc.device))
-        _cabi.check(rc, "q4b_gemv_gather")
-        self._gather_hdl.barrier()                      # every rank's stores have landed
-        return self._gather_buf[:M]
+        return self._gather.gemv(x, Q.prepack_ggml_q4_0(self.weight_blocks))
 
 
 class FusedGatherBuffer:
-    """The gathered output ``[max_rows, N]`` of a column-parallel decode product in symmetric memory
-    (peer-mapped on every rank), and the launch that fills it: each rank's decode kernel stores its
-    ``[M, N/g]`` columns into every rank's buffer over NVLink (plain peer stores), with a
-    symmetric-memory barrier on the stream before (nobody still reads the previous result) and after
-    (every rank's stores have landed).  Takes the weight per call, so one buffer serves many layers
+    """The gathered output of a column-parallel decode product without a collective: each rank's decode
+    kernel stores its ``[M, N/g]`` columns into every rank's buffer over NVLink (plain peer stores of
+    self-validating words, no TMA, no multicast) and a small kernel on each rank waits for them, bounded,
+    and writes the plain ``[M, N]`` result.  Takes the weight per call, so one buffer serves many layers
     of the same width."""
 
     def __init__(self, N: int, rank: int, world: int, dtype: torch.dtype, device, group=None, max_rows: int = 16):
-        import torch.distributed._symmetric_memory as symm_mem
         if N % world:
             raise RuntimeError("fused gather needs N divisible by the number of ranks")
-        self.N, self.rank, self.world, self.n0 = N, rank, world, rank * (N // world)
-        group = group if group is not None else dist.group.WORLD
-        self.buf = symm_mem.empty((max_rows, N), dtype=dtype, device=device)
-        self.hdl = symm_mem.rendezvous(self.buf, group)
-        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.N, self.rank, self.world, self.n0, self.dtype = N, rank, world, rank * (N // world), dtype
+        self.ex = _PeerExchange(max_rows, N, device, group)
 
     def gemv(self, x: torch.Tensor, pre: "Q.Q4Prepacked") -> torch.Tensor:
-        import ctypes
         from . import _cabi
         M = x.shape[0]
-        if M > self.buf.shape[0] or M > 16 or x.dtype != self.buf.dtype or pre.N != self.N // self.world:
+        if M > self.ex.max_rows or M > 16 or x.dtype != self.dtype or pre.N != self.N // self.world:
             raise RuntimeError("fused gather: up to 16 rows of the buffer's dtype, weight shard of N / world columns")
         xc = x.contiguous()
-        self.hdl.barrier()
-        ptrs = (ctypes.c_void_p * self.world)(*self.ptrs)
+        ptrs, local, epoch = self.ex.next()
+        out = torch.empty((M, self.N), dtype=x.dtype, device=x.device)
         with torch.cuda.device(xc.device):
-            rc = _cabi.load().q4b_gemv_gather(xc.data_ptr(), _cabi.DTYPE_CODE[xc.dtype], M, xc.stride(0), pre.data.data_ptr(),
-                                              pre.K, pre.N, ptrs, self.world, self.n0, self.N, 0, _cabi.stream_ptr(xc.device))
-        _cabi.check(rc, "q4b_gemv_gather")
-        self.hdl.barrier()
-        return self.buf[:M]
+            rc = _cabi.load().q4b_gemv_exchange(xc.data_ptr(), _cabi.DTYPE_CODE[xc.dtype], M, xc.stride(0), pre.data.data_ptr(),
+                                                pre.K, pre.N, ptrs, self.world, self.n0, self.N, local, 1, epoch,
+                                                out.data_ptr(), out.stride(0), 0, _cabi.stream_ptr(xc.device))
+        _cabi.check(rc, "q4b_gemv_exchange")
+        return out
 
 
 class RowParallelQ4Linear(nn.Module):
@@ -196,34 +200,28 @@ class RowParallelQ4Linear(nn.Module):
 
     # ---- fused reduction for decode (M <= 16) ----
     def enable_fused_reduce(self, max_rows: int = 16, dtype: torch.dtype = torch.float16) -> None:
-        """Allocate ``[max_rows, world * N]`` in symmetric memory: slot r of every rank's buffer
+        """Allocate ``2 x [max_rows, world * N]`` in symmetric memory: slot r of every rank's buffer
         receives rank r's partial product."""
-        import torch.distributed._symmetric_memory as symm_mem
-        dev = self.weight_blocks.device
-        group = self.group if self.group is not None else dist.group.WORLD
-        self._red_buf = symm_mem.empty((max_rows, self.world * self.N), dtype=dtype, device=dev)
-        self._red_hdl = symm_mem.rendezvous(self._red_buf, group)
-        self._red_ptrs = [int(p) for p in self._red_hdl.buffer_ptrs]
+        self._red = _PeerExchange(max_rows, self.world * self.N, self.weight_blocks.device, self.group)
+        self._red_dtype = dtype
 
     def forward_fused_reduce(self, x: torch.Tensor) -> torch.Tensor:
         """``[M, N]`` on every rank, M <= 16: the decode kernel of each rank writes its partial
-        product into slot ``rank`` of all ranks' buffers over NVLink (q4b_gemv_gather); after a
-        symmetric-memory barrier every rank adds the slots in rank order, in fp32."""
-        import ctypes
+        product into slot ``rank`` of all ranks' buffers over NVLink (self-validating words, no barrier);
+        a small kernel on each rank waits for the ``world`` slots and adds them in rank order, in fp32."""
         from . import _cabi
-        if getattr(self, "_red_hdl", None) is None:
+        if getattr(self, "_red", None) is None:
             raise RuntimeError("call enable_fused_reduce() first")
         xl = self._local_x(x).contiguous()
         M = xl.shape[0]
-        if M > self._red_buf.shape[0] or M > 16 or xl.dtype != self._red_buf.dtype:
+        if M > self._red.max_rows or M > 16 or xl.dtype != self._red_dtype:
             raise RuntimeError("fused reduce serves up to 16 rows of the dtype it was enabled for")
         pre = Q.prepack_ggml_q4_0(self.weight_blocks)
-        self._red_hdl.barrier()                         # nobody still reads the previous partials
-        ptrs = (ctypes.c_void_p * self.world)(*self._red_ptrs)
+        ptrs, local, epoch = self._red.next()
+        out = torch.empty((M, self.N), dtype=xl.dtype, device=xl.device)
         with torch.cuda.device(xl.device):
-            rc = _cabi.load().q4b_gemv_gather(xl.data_ptr(), _cabi.DTYPE_CODE[xl.dtype], M, xl.stride(0), pre.data.data_ptr(),
-                                              pre.K, pre.N, ptrs, self.world, self.rank * self.N, self.world * self.N, 0,
-                                              _cabi.stream_ptr(xl.device))
-        _cabi.check(rc, "q4b_gemv_gather")
-        self._red_hdl.barrier()                         # every rank's partial has landed
-        return self._red_buf[:M].view(M, self.world, self.N).float().sum(dim=1).to(xl.dtype)
+            rc = _cabi.load().q4b_gemv_exchange(xl.data_ptr(), _cabi.DTYPE_CODE[xl.dtype], M, xl.stride(0), pre.data.data_ptr(),
+                                                pre.K, pre.N, ptrs, self.world, self.rank * self.N, self.world * self.N, local,
+                                                self.world, epoch, out.data_ptr(), out.stride(0), 0, _cabi.stream_ptr(xl.device))
+        _cabi.check(rc, "q4b_gemv_exchange")
+        return out

@@ -41,10 +41,10 @@ def _worker(rank: int, world: int, port: int, ret):
                     layer.enable_fused_gather(max_rows=16, dtype=dt)
                     fused_layer = layer
                 else:
-                    layer._gather_buf, layer._gather_hdl, layer._gather_ptrs = (fused_layer._gather_buf, fused_layer._gather_hdl,
-                                                                               fused_layer._gather_ptrs)
-                y_fused = layer.forward_fused_gather(x)
-                ok &= bool(torch.equal(y_fused, y_full))
+                    layer._gather = fused_layer._gather          # one pair of exchange buffers serves layers of one width
+                for _ in range(5):                               # several calls: both buffers, advancing epochs
+                    y_fused = layer.forward_fused_gather(x)
+                    ok &= bool(torch.equal(y_fused, y_full))
         # row-parallel (k-sharded) layer: NCCL all-reduce and the fused reduction against one GPU
         K2, N2 = 2048, 1000
         w2 = (torch.randn(K2, N2, generator=g) * 0.02).to(dev)
@@ -53,9 +53,11 @@ def _worker(rank: int, world: int, port: int, ret):
         for M in (1, 7):
             x2 = torch.randn(M, K2, generator=g).half().to(dev)
             ref2 = mo.matmul_ggml_q4_0(x2, mo.quantize_ggml_q4_0(w2)).float()
-            for y2 in (row(x2), row.forward_fused_reduce(x2)):
+            for y2 in (row(x2), row.forward_fused_reduce(x2), row.forward_fused_reduce(x2), row.forward_fused_reduce(x2)):
                 ok &= tuple(y2.shape) == (M, N2)
                 ok &= bool(((y2.float() - ref2).norm() / ref2.norm()).item() <= 2e-3)
+        from metalops_b200 import quantization as Q
+        ok &= Q.wait_status(dev) == 0
         torch.cuda.synchronize()
         ret[rank] = bool(ok)
     finally:
@@ -107,3 +109,54 @@ def test_fused_gather_kernel_on_one_gpu(M, dtype):
                                         ptrs, 9, 0, N, 0, _cabi.stream_ptr(dev)) != 0
     assert _cabi.load().q4b_gemv_gather(x.data_ptr(), _cabi.DTYPE_CODE[dtype], M, x.stride(0), pre.data.data_ptr(), K, 1200,
                                         ptrs, world, 1300, N, 0, _cabi.stream_ptr(dev)) != 0
+
+
+@pytest.mark.parametrize("M,dtype", [(1, torch.float16), (9, torch.bfloat16)])
+def test_barrier_free_gather_on_one_gpu(M, dtype):
+    """The self-validating-word form of the gather with two ranks' shards run as launches on one GPU: both
+    store (value | epoch) words into both ranks' buffers, the unpack kernel then finds every word of the
+    epoch and returns the local products side by side, bit for bit; as partial sums (slots = 2) it adds
+    them in fp32.  A buffer that never receives its epoch makes the bounded wait run out: status 700,
+    zeros returned, and the next product is fine."""
+    import ctypes
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import metalops_b200 as mo
+    from metalops_b200 import _cabi, quantization as Q
+    lib = _cabi.load()
+    dev = torch.device("cuda:0")
+    sp = _cabi.stream_ptr(dev)
+    g = torch.Generator().manual_seed(78)
+    K, N, world = 1056, 2 * 1200, 2
+    w = (torch.randn(K, N, generator=g) * 0.02).to(dev)
+    x = torch.randn(M, K, generator=g).to(dtype).to(dev)
+    code = _cabi.DTYPE_CODE[dtype]
+    lls = [torch.zeros(M, N, dtype=torch.int32, device=dev) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in lls])
+    for epoch in (1, 2, 65535):
+        locals_ = []
+        for r in range(world):
+            n0, n1 = mo.shard_bounds(N, world, r)
+            pre = mo.prepack_ggml_q4_0(mo.quantize_ggml_q4_0(w[:, n0:n1].contiguous()))
+            assert lib.q4b_gemv_gather_ll(x.data_ptr(), code, M, x.stride(0), pre.data.data_ptr(), K, n1 - n0, ptrs, world, n0, N,
+                                          epoch, 0, sp) == 0
+            locals_.append(Q._matmul_prepacked(x, pre, kernel="gemv"))
+        full = torch.cat(locals_, dim=1)
+        for t in lls:
+            out = torch.empty(M, N, dtype=dtype, device=dev)
+            assert lib.q4b_gather_ll_unpack(t.data_ptr(), M, N, N, 1, epoch, code, out.data_ptr(), N, sp) == 0
+            assert torch.equal(out, full)
+        # the two halves of a row as two partial results
+        summed = torch.empty(M, N // 2, dtype=dtype, device=dev)
+        assert lib.q4b_gather_ll_unpack(lls[0].data_ptr(), M, N // 2, N, 2, epoch, code, summed.data_ptr(), N // 2, sp) == 0
+        assert torch.equal(summed, (locals_[0].float() + locals_[1].float()).to(dtype))
+    assert Q.wait_status(dev) == 0
+    # nobody stores epoch 7: the wait gives up after a fraction of a second
+    out = torch.full((M, N), 3.0, dtype=dtype, device=dev)
+    assert lib.q4b_gather_ll_unpack(lls[0].data_ptr(), M, 64, N, 1, 7, code, out.data_ptr(), N, sp) == 0
+    detail = ctypes.c_int(0)
+    assert lib.q4b_wait_status(sp, ctypes.byref(detail)) == _cabi.ERR_TIMEOUT and detail.value == 700
+    assert float(out[:, :64].abs().max()) == 0.0
+    assert Q.wait_status(dev) == 0
+    assert torch.equal(Q._matmul_prepacked(x, pre, kernel="gemv"), locals_[1])
+    assert lib.q4b_gemv_gather_ll(x.data_ptr(), code, M, x.stride(0), pre.data.data_ptr(), K, 1200, ptrs, world, 0, N, 0, 0, sp) != 0
