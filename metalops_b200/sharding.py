@@ -70,6 +70,12 @@ class _PeerExchange:
 
     def next(self):
         """(peer pointers of this call's buffer, address of this rank's own, epoch)"""
+        if self.calls and self.calls % 65535 == 0:
+            # the 16-bit epoch starts over: clear both buffers on every rank first (all ranks get here on the same
+            # call), so that a row no recent call has written cannot carry the same epoch from 65535 calls ago
+            self.hdl.barrier()
+            self.buf.zero_()
+            self.hdl.barrier()
         par = self.calls & 1
         epoch = self.calls % 65535 + 1
         self.calls += 1
