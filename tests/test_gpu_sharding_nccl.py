@@ -44,7 +44,8 @@ def _worker(rank: int, world: int, port: int, ret):
                     layer._gather = fused_layer._gather          # one pair of exchange buffers serves layers of one width
                 for it in range(9):                              # several calls: both buffers, advancing epochs
                     if it == 5:
-                        layer._gather.ex.calls = 65533           # the same on every rank: the 16-bit epoch starts over
+                        ex = layer._gather.ex                    # the same on every rank: the 16-bit epoch starts over soon
+                        ex.calls = 65533 if ex.calls & 1 else 65534      # (keeping the alternation of the two buffers)
                     y_fused = layer.forward_fused_gather(x)
                     ok &= bool(torch.equal(y_fused, y_full))
         # row-parallel (k-sharded) layer: NCCL all-reduce and the fused reduction against one GPU
