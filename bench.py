@@ -772,8 +772,8 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
     from metalops_b200 import quantization as Q
     from metalops_b200 import sharding as S
     res = {"world": world, "scaling": "strong",
-           "note": "algorithmic bytes / flops of the WHOLE layer over the slowest rank's device time; `local` runs as a CUDA "
-                   "graph, the variants with a collective are enqueued call by call from Python (host-driven)"}
+           "note": "algorithmic bytes / flops of the WHOLE layer over the slowest rank's device time; `local` and the `_graph` "
+                   "entries replay a CUDA graph, the other variants are enqueued call by call from Python (host-driven)"}
 
     def max_over_ranks(ms):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -821,6 +821,8 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
                             fused.gemv(x, pres[i % len(pres)])
                         dist.barrier()
                         e["fused_peer_store_gather"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, fused_step, reps, graph=False)))
+                        dist.barrier()
+                        e["fused_peer_store_gather_graph"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, fused_step, reps)))
                     except Exception as ex:           # symmetric memory unavailable on this box
                         e["fused_peer_store_gather"] = {"error": str(ex)[:200]}
             entry[f"column_parallel_m{M}"] = e
@@ -859,15 +861,11 @@ def bench_sharded(dev, stream, lib, rank, world, peaks):
                             out = torch.empty(M, N, device=dev, dtype=torch.float16)
 
                             def fused_reduce(i, x=x, ex=ex, out=out):
-                                p = pres[i % len(pres)]
-                                ptrs, local_ll, epoch = ex.next()
-                                rc = lib.q4b_gemv_exchange(x.data_ptr(), _cabi.F16, 1, k_loc, p.data.data_ptr(), k_loc, N, ptrs, world,
-                                                           rank * N, world * N, local_ll, world, epoch, out.data_ptr(), N, 0,
-                                                           torch.cuda.current_stream(dev).cuda_stream)
-                                if rc:
-                                    _cabi.check(rc, "q4b_gemv_exchange")
+                                ex.run(x, pres[i % len(pres)], world, rank * N, world, out)
                             dist.barrier()
                             e["fused_peer_store_reduce"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, fused_reduce, reps, graph=False)))
+                            dist.barrier()
+                            e["fused_peer_store_reduce_graph"] = whole_job(M, K, N, max_over_ranks(time_launches(stream, fused_reduce, reps)))
                         except Exception as ex_:          # symmetric memory unavailable on this box
                             e["fused_peer_store_reduce"] = {"error": str(ex_)[:200]}
                 entry[f"row_parallel_m{M}"] = e

@@ -342,6 +342,15 @@ Q4B_API int q4b_gemv_exchange(const void *x, int x_dtype, int64_t M, int64_t ldx
                               int64_t N, void *const *ll_ranks, int world, int64_t col0, int64_t ld_out,
                               const void *ll_local, int slots, int epoch, void *out, int64_t ld_y, int flags,
                               void *stream);
+/* The same with the call counter in device memory, so that nothing changes on the host from call to call
+ * and a captured launch can be replayed: ctl points at two ints (zero at set-up, one pair per rank), call c
+ * uses epoch c % 65535 + 1 and the buffer of parity c & 1; a rank's two buffers are ll_half words apart and
+ * ll_ranks / ll_local point at the first.  The unpack kernel sets the words it read back to zero (nothing
+ * stale survives a call) and its last block increments the counter. */
+Q4B_API int q4b_gemv_exchange_dev(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked,
+                                  int64_t K, int64_t N, void *const *ll_ranks, int world, int64_t col0,
+                                  int64_t ld_out, void *ll_local, int64_t ll_half, int slots, int *ctl, void *out,
+                                  int64_t ld_y, int flags, void *stream);
 
 /*
  * RMSNorm in front of a quantised linear layer, the first step of the reference's

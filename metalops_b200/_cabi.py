@@ -56,6 +56,8 @@ SYMBOLS = {
     "q4b_gemv_gather": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _vp]),
     "q4b_gemv_gather_ll": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _ci, _ci, _vp]),
     "q4b_gather_ll_unpack": (_ci, [_vp, _i64, _i64, _i64, _ci, _ci, _ci, _vp, _i64, _vp]),
+    "q4b_gemv_exchange_dev": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _vp, _i64, _ci, _vp,
+                                    _vp, _i64, _ci, _vp]),
     "q4b_gemv_exchange": (_ci, [_vp, _ci, _i64, _i64, _vp, _i64, _i64, ctypes.POINTER(_vp), _ci, _i64, _i64, _vp, _ci, _ci, _vp, _i64,
                                 _ci, _vp]),
     "q4b_import_ggml": (_ci, [_vp, _i64, _i64, _vp, _vp]),

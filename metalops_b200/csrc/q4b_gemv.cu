@@ -46,7 +46,22 @@ struct PeerOut {
     // ll_tag != 0: the peers' buffers hold 32-bit words and each store is (value | ll_tag), the tag being
     // the call's epoch in the upper half: a word validates itself, so the reader needs no barrier.
     uint32_t ll_tag;
+    // ll_ctl != null: the call counter lives in device memory (so a captured launch can be replayed): call c
+    // uses epoch c % 65535 + 1 and the buffer of parity c & 1, which starts ll_half words after p[r].
+    const int *ll_ctl;
+    int64_t ll_half;
 };
+
+// (tag, word offset of this call's buffer) of a self-validating store
+__device__ __forceinline__ void ll_call(const PeerOut &peers, uint32_t &tag, int64_t &base) {
+    tag = peers.ll_tag;
+    base = 0;
+    if (peers.ll_ctl != nullptr) {
+        const int c = *reinterpret_cast<const volatile int *>(peers.ll_ctl);
+        tag = (uint32_t)(c % 65535 + 1) << 16;
+        base = (c & 1) ? peers.ll_half : 0;
+    }
+}
 
 
 // Shared-memory geometry of one ring slot: CHUNK weight tiles, then the x rows.  The row
@@ -375,8 +390,14 @@ gemv_kernel(const uint16_t *__restrict__ x, int M, int64_t ldx, const uint8_t *_
                 for (int r = 0; r < 8; ++r)        // static indices: the pointers stay in the parameter bank
                     if (r < peers.world) {
                         const size_t at = (size_t)m * peers.ld + peers.col0 + n;
-                        if (peers.ll_tag != 0) reinterpret_cast<uint32_t *>(peers.p[r])[at] = (uint32_t)bits | peers.ll_tag;
-                        else peers.p[r][at] = bits;
+                        if (peers.ll_tag != 0 || peers.ll_ctl != nullptr) {
+                            uint32_t tag;
+                            int64_t base;
+                            ll_call(peers, tag, base);
+                            reinterpret_cast<uint32_t *>(peers.p[r])[base + at] = (uint32_t)bits | tag;
+                        } else {
+                            peers.p[r][at] = bits;
+                        }
                     }
             }
         }
@@ -606,8 +627,14 @@ gemv_m1_kernel(const uint16_t *__restrict__ x, const uint8_t *__restrict__ prepa
 #pragma unroll
                 for (int r = 0; r < 8; ++r)        // static indices: the pointers stay in the parameter bank
                     if (r < peers.world) {
-                        if (peers.ll_tag != 0) reinterpret_cast<uint32_t *>(peers.p[r])[peers.col0 + n] = (uint32_t)bits | peers.ll_tag;
-                        else peers.p[r][peers.col0 + n] = bits;
+                        if (peers.ll_tag != 0 || peers.ll_ctl != nullptr) {
+                            uint32_t tag;
+                            int64_t base;
+                            ll_call(peers, tag, base);
+                            reinterpret_cast<uint32_t *>(peers.p[r])[base + peers.col0 + n] = (uint32_t)bits | tag;
+                        } else {
+                            peers.p[r][peers.col0 + n] = bits;
+                        }
                     }
             }
         }
@@ -719,17 +746,24 @@ static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const v
 // (bounded: code 700 and zeros on giving up), then writes the plain values.  SLOTS > 1: the row holds SLOTS
 // partial results side by side (one per rank), summed here in fp32 in slot order and rounded once.
 constexpr long long LL_WAIT_CYCLES = 1LL << 29;      // ~0.3 s
+// ctl != null: ctl[0] is the call counter (see PeerOut), ctl[1] counts the blocks that are done; the words
+// read are set back to 0 (no epoch), so nothing stale survives a call, and the last block out bumps ctl[0].
 template <bool BF16, bool SUM>
 __global__ void __launch_bounds__(256)
-ll_unpack_kernel(const uint32_t *ll, int rows, int64_t cols, int64_t ld_ll, int slots, uint32_t tag, uint16_t *__restrict__ out,
-                 int64_t ld_out) {
+ll_unpack_kernel(uint32_t *ll, int rows, int64_t cols, int64_t ld_ll, int slots, uint32_t tag, uint16_t *__restrict__ out,
+                 int64_t ld_out, int *ctl, int64_t ll_half) {
+    if (ctl != nullptr) {
+        const int c = *reinterpret_cast<const volatile int *>(ctl);
+        tag = (uint32_t)(c % 65535 + 1) << 16;
+        if (c & 1) ll += ll_half;
+    }
     const int64_t total = (int64_t)rows * cols;
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
         const int64_t m = i / cols, n = i % cols;
         float acc = 0.0f;
         uint32_t last = 0;
         for (int sl = 0; sl < slots; ++sl) {
-            const uint32_t *w = ll + m * ld_ll + (int64_t)sl * cols + n;
+            uint32_t *w = ll + m * ld_ll + (int64_t)sl * cols + n;
             uint32_t v;
             long long t0 = 0;
             for (int it = 0;; ++it) {
@@ -747,9 +781,21 @@ ll_unpack_kernel(const uint32_t *ll, int rows, int64_t cols, int64_t ld_ll, int 
                 }
             }
             last = v & 0xFFFFu;
+            if (ctl != nullptr) *w = 0;
             if (SUM) acc += BF16 ? __bfloat162float(__ushort_as_bfloat16((uint16_t)last)) : __half2float(__ushort_as_half((uint16_t)last));
         }
         out[m * ld_out + n] = SUM ? out_bits<BF16>(acc) : (uint16_t)last;
+    }
+    if (ctl != nullptr) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(&ctl[1], 1) == (int)gridDim.x - 1) {      // the last block out: the next call's counter
+                ctl[1] = 0;
+                __threadfence();
+                atomicAdd(&ctl[0], 1);
+            }
+        }
     }
 }
 
@@ -817,6 +863,21 @@ extern "C" int q4b_int4g_gemv(const void *x, int x_dtype, int64_t M, int64_t ldx
     return gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, bias, 0, y, ldy, flags, stream, po);
 }
 
+static int launch_ll_unpack(const void *ll, int64_t rows, int64_t cols, int64_t ld_ll, int slots, uint32_t tag, int x_dtype, void *out,
+                            int64_t ld_out, int *ctl, int64_t ll_half, cudaStream_t st) {
+    const int64_t total = rows * cols;
+    const unsigned grid = (unsigned)(ceil_div(total, 256) < 1184 ? ceil_div(total, 256) : 1184);
+    uint32_t *w = (uint32_t *)const_cast<void *>(ll);
+    if (slots == 1)
+        ll_unpack_kernel<false, false><<<grid, 256, 0, st>>>(w, (int)rows, cols, ld_ll, 1, tag, (uint16_t *)out, ld_out, ctl, ll_half);
+    else if (x_dtype == Q4B_BF16)
+        ll_unpack_kernel<true, true><<<grid, 256, 0, st>>>(w, (int)rows, cols, ld_ll, slots, tag, (uint16_t *)out, ld_out, ctl, ll_half);
+    else
+        ll_unpack_kernel<false, true><<<grid, 256, 0, st>>>(w, (int)rows, cols, ld_ll, slots, tag, (uint16_t *)out, ld_out, ctl, ll_half);
+    Q4B_LAUNCH_CHECK();
+    return Q4B_OK;
+}
+
 // The gather without barriers: the peers' buffers are uint32 [rows, ld_out] and every store carries the call's
 // epoch (1..65535) in its upper half; q4b_gather_ll_unpack on each rank waits, word by word and bounded, for
 // all words of the epoch and writes the plain result.  The caller alternates between two buffers from call
@@ -844,18 +905,31 @@ extern "C" int q4b_gather_ll_unpack(const void *ll, int64_t rows, int64_t cols, 
     if (ll == nullptr || out == nullptr || rows < 1 || rows > 16 || cols < 1 || slots < 1 || slots > 8) return Q4B_ERR_ARG;
     if (ld_ll < (int64_t)slots * cols || ld_out < cols || epoch < 1 || epoch > 65535) return Q4B_ERR_ARG;
     if (x_dtype != Q4B_F16 && x_dtype != Q4B_BF16) return Q4B_ERR_DTYPE;
-    const int64_t total = rows * cols;
-    const unsigned grid = (unsigned)(ceil_div(total, 256) < 1184 ? ceil_div(total, 256) : 1184);
-    const uint32_t tag = (uint32_t)epoch << 16;
-    cudaStream_t st = (cudaStream_t)stream;
-    if (slots == 1)
-        ll_unpack_kernel<false, false><<<grid, 256, 0, st>>>((const uint32_t *)ll, (int)rows, cols, ld_ll, 1, tag, (uint16_t *)out, ld_out);
-    else if (x_dtype == Q4B_BF16)
-        ll_unpack_kernel<true, true><<<grid, 256, 0, st>>>((const uint32_t *)ll, (int)rows, cols, ld_ll, slots, tag, (uint16_t *)out, ld_out);
-    else
-        ll_unpack_kernel<false, true><<<grid, 256, 0, st>>>((const uint32_t *)ll, (int)rows, cols, ld_ll, slots, tag, (uint16_t *)out, ld_out);
-    Q4B_LAUNCH_CHECK();
-    return Q4B_OK;
+    return launch_ll_unpack(ll, rows, cols, ld_ll, slots, (uint32_t)epoch << 16, x_dtype, out, ld_out, nullptr, 0, (cudaStream_t)stream);
+}
+
+// The exchange with the call counter in device memory (ctl: two ints, zero at set-up; the two buffers of a
+// rank are ll_half words apart, ll_ranks / ll_local point at the first): nothing changes from call to call on
+// the host side, so a captured launch can be replayed.  The unpack sets the words it read back to zero.
+extern "C" int q4b_gemv_exchange_dev(const void *x, int x_dtype, int64_t M, int64_t ldx, const void *prepacked, int64_t K, int64_t N,
+                                     void *const *ll_ranks, int world, int64_t col0, int64_t ld_out, void *ll_local, int64_t ll_half,
+                                     int slots, int *ctl, void *out, int64_t ld_y, int flags, void *stream) {
+    if (ll_ranks == nullptr || world < 1 || world > 8 || col0 < 0 || ld_out < col0 + N || ctl == nullptr || ll_half < 16 * ld_out)
+        return Q4B_ERR_ARG;
+    if (ll_local == nullptr || out == nullptr || slots < 1 || slots > 8 || M < 1 || M > 16) return Q4B_ERR_ARG;
+    for (int r = 0; r < world; ++r)
+        if (ll_ranks[r] == nullptr || !aligned(ll_ranks[r], 4)) return Q4B_ERR_ARG;
+    PeerOut po = {};
+    for (int r = 0; r < world; ++r) po.p[r] = (uint16_t *)ll_ranks[r];
+    po.world = world;
+    po.col0 = col0;
+    po.ld = ld_out;
+    po.ll_ctl = ctl;
+    po.ll_half = ll_half;
+    if (int rc = gemv_dispatch(x, x_dtype, M, ldx, prepacked, K, N, nullptr, 0, ll_ranks[0], ld_out, flags, stream, po)) return rc;
+    const int64_t cols = slots > 1 ? N : ld_out;
+    if (ld_out < (int64_t)slots * cols || ld_y < cols) return Q4B_ERR_ARG;
+    return launch_ll_unpack(ll_local, M, cols, ld_out, slots, 0, x_dtype, out, ld_y, ctl, ll_half, (cudaStream_t)stream);
 }
 
 // Both steps of the barrier-free exchange in one call: the product stored into every rank's words, then the

@@ -46,40 +46,39 @@ def gather_columns(y_local: torch.Tensor, group=None, world: Optional[int] = Non
 
 
 class _PeerExchange:
-    """Two ``[max_rows, width]`` uint32 buffers in symmetric memory (peer-mapped on every rank) and the epoch
-    counter of the barrier-free exchange: a decode kernel stores (value | epoch << 16) into every rank's
-    buffer (q4b_gemv_gather_ll), and each rank's q4b_gather_ll_unpack waits, word by word and bounded, for
-    the epoch.  Calls alternate between the two buffers, so with every rank running its calls in stream
-    order nobody can still be reading the buffer that a peer overwrites.  The one barrier is at set-up."""
+    """Two ``[max_rows, width]`` uint32 buffers in symmetric memory (peer-mapped on every rank) and the
+    device-resident call counter of the barrier-free exchange (q4b_gemv_exchange_dev): a decode kernel stores
+    (value | epoch << 16) into every rank's buffer and each rank's unpack kernel waits, word by word and
+    bounded, for the epoch, clears what it read and bumps the counter.  Calls alternate between the two
+    buffers, so with every rank running its calls in stream order nobody can still be reading the buffer
+    that a peer overwrites.  The one barrier is at set-up; nothing changes on the host between calls, so a
+    call can be captured in a CUDA graph and replayed."""
 
     def __init__(self, max_rows: int, width: int, device, group=None):
+        import ctypes
         import torch.distributed._symmetric_memory as symm_mem
         group = group if group is not None else dist.group.WORLD
-        self.max_rows, self.width = max_rows, width
-        self.buf = symm_mem.empty((2, max_rows, width), dtype=torch.int32, device=device)
-        self.buf.zero_()                                     # epoch 0 is never used
+        self.max_rows, self.width = max(16, max_rows), width
+        self.buf = symm_mem.empty((2, self.max_rows, width), dtype=torch.int32, device=device)
+        self.buf.zero_()                                     # no epoch anywhere
+        self.ctl = torch.zeros(2, dtype=torch.int32, device=device)
         self.hdl = symm_mem.rendezvous(self.buf, group)
         torch.cuda.synchronize(device)
         self.hdl.barrier()                                   # every rank's buffers are cleared before anyone stores
-        half = max_rows * width * 4
-        import ctypes
-        self.ptrs = [(ctypes.c_void_p * len(self.hdl.buffer_ptrs))(*[int(p) + par * half for p in self.hdl.buffer_ptrs])
-                     for par in (0, 1)]
-        self.local = [self.buf[0].data_ptr(), self.buf[1].data_ptr()]
-        self.calls = 0
+        self.half_words = self.max_rows * width
+        self.ptrs = (ctypes.c_void_p * len(self.hdl.buffer_ptrs))(*[int(p) for p in self.hdl.buffer_ptrs])
+        self.local = self.buf.data_ptr()
 
-    def next(self):
-        """(peer pointers of this call's buffer, address of this rank's own, epoch)"""
-        if self.calls and self.calls % 65535 == 0:
-            # the 16-bit epoch starts over: clear both buffers on every rank first (all ranks get here on the same
-            # call), so that a row no recent call has written cannot carry the same epoch from 65535 calls ago
-            self.hdl.barrier()
-            self.buf.zero_()
-            self.hdl.barrier()
-        par = self.calls & 1
-        epoch = self.calls % 65535 + 1
-        self.calls += 1
-        return self.ptrs[par], self.local[par], epoch
+    def run(self, x: torch.Tensor, pre: "Q.Q4Prepacked", world: int, col0: int, slots: int, out: torch.Tensor) -> None:
+        """One exchange: the product of ``x`` with this rank's weight stored at column ``col0`` of every rank's
+        buffer, then this rank's unpack into ``out`` (slots == 1: the gathered row; else the sum of the slots)."""
+        from . import _cabi
+        with torch.cuda.device(x.device):
+            rc = _cabi.load().q4b_gemv_exchange_dev(x.data_ptr(), _cabi.DTYPE_CODE[x.dtype], x.shape[0], x.stride(0),
+                                                    pre.data.data_ptr(), pre.K, pre.N, self.ptrs, world, col0, self.width,
+                                                    self.local, self.half_words, slots, self.ctl.data_ptr(), out.data_ptr(),
+                                                    out.stride(0), 0, _cabi.stream_ptr(x.device))
+        _cabi.check(rc, "q4b_gemv_exchange_dev")
 
 
 class ColumnParallelQ4Linear(nn.Module):
@@ -150,13 +149,8 @@ class FusedGatherBuffer:
         if M > self.ex.max_rows or M > 16 or x.dtype != self.dtype or pre.N != self.N // self.world:
             raise RuntimeError("fused gather: up to 16 rows of the buffer's dtype, weight shard of N / world columns")
         xc = x.contiguous()
-        ptrs, local, epoch = self.ex.next()
         out = torch.empty((M, self.N), dtype=x.dtype, device=x.device)
-        with torch.cuda.device(xc.device):
-            rc = _cabi.load().q4b_gemv_exchange(xc.data_ptr(), _cabi.DTYPE_CODE[xc.dtype], M, xc.stride(0), pre.data.data_ptr(),
-                                                pre.K, pre.N, ptrs, self.world, self.n0, self.N, local, 1, epoch,
-                                                out.data_ptr(), out.stride(0), 0, _cabi.stream_ptr(xc.device))
-        _cabi.check(rc, "q4b_gemv_exchange")
+        self.ex.run(xc, pre, self.world, self.n0, 1, out)
         return out
 
 
@@ -223,11 +217,6 @@ class RowParallelQ4Linear(nn.Module):
         if M > self._red.max_rows or M > 16 or xl.dtype != self._red_dtype:
             raise RuntimeError("fused reduce serves up to 16 rows of the dtype it was enabled for")
         pre = Q.prepack_ggml_q4_0(self.weight_blocks)
-        ptrs, local, epoch = self._red.next()
         out = torch.empty((M, self.N), dtype=xl.dtype, device=xl.device)
-        with torch.cuda.device(xl.device):
-            rc = _cabi.load().q4b_gemv_exchange(xl.data_ptr(), _cabi.DTYPE_CODE[xl.dtype], M, xl.stride(0), pre.data.data_ptr(),
-                                                pre.K, pre.N, ptrs, self.world, self.rank * self.N, self.world * self.N, local,
-                                                self.world, epoch, out.data_ptr(), out.stride(0), 0, _cabi.stream_ptr(xl.device))
-        _cabi.check(rc, "q4b_gemv_exchange")
+        self._red.run(xl, pre, self.world, self.rank * self.N, self.world, out)
         return out

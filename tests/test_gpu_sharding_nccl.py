@@ -45,7 +45,8 @@ def _worker(rank: int, world: int, port: int, ret):
                 for it in range(9):                              # several calls: both buffers, advancing epochs
                     if it == 5:
                         ex = layer._gather.ex                    # the same on every rank: the 16-bit epoch starts over soon
-                        ex.calls = 65533 if ex.calls & 1 else 65534      # (keeping the alternation of the two buffers)
+                        c = int(ex.ctl[0].item())                # (keeping the alternation of the two buffers)
+                        ex.ctl[0] = 65533 if c & 1 else 65534
                     y_fused = layer.forward_fused_gather(x)
                     ok &= bool(torch.equal(y_fused, y_full))
         # row-parallel (k-sharded) layer: NCCL all-reduce and the fused reduction against one GPU
@@ -59,6 +60,20 @@ def _worker(rank: int, world: int, port: int, ret):
             for y2 in (row(x2), row.forward_fused_reduce(x2), row.forward_fused_reduce(x2), row.forward_fused_reduce(x2)):
                 ok &= tuple(y2.shape) == (M, N2)
                 ok &= bool(((y2.float() - ref2).norm() / ref2.norm()).item() <= 2e-3)
+        # a captured exchange replays: the call counter lives on the device
+        xg = torch.randn(1, K2, generator=g).half().to(dev)
+        refg = row(xg)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            row.forward_fused_reduce(xg)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                yg = row.forward_fused_reduce(xg)
+            for _ in range(3):
+                graph.replay()
+        side.synchronize()
+        ok &= bool(((yg.float() - refg.float()).norm() / refg.float().norm()).item() <= 2e-3)
         from metalops_b200 import quantization as Q
         ok &= Q.wait_status(dev) == 0
         torch.cuda.synchronize()
@@ -163,3 +178,47 @@ def test_barrier_free_gather_on_one_gpu(M, dtype):
     assert Q.wait_status(dev) == 0
     assert torch.equal(Q._matmul_prepacked(x, pre, kernel="gemv"), locals_[1])
     assert lib.q4b_gemv_gather_ll(x.data_ptr(), code, M, x.stride(0), pre.data.data_ptr(), K, 1200, ptrs, world, 0, N, 0, 0, sp) != 0
+
+
+def test_exchange_with_device_counter_on_one_gpu():
+    """q4b_gemv_exchange_dev with one rank: the counter advances by one per call, the buffers alternate, the
+    words that were read are cleared, and a captured call replays."""
+    import ctypes
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import metalops_b200 as mo
+    from metalops_b200 import _cabi, quantization as Q
+    lib = _cabi.load()
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(79)
+    K, N, M = 1056, 1200, 3
+    pre = mo.prepack_ggml_q4_0(mo.quantize_ggml_q4_0((torch.randn(K, N, generator=g) * 0.02).to(dev)))
+    x = torch.randn(M, K, generator=g).half().to(dev)
+    ref = Q._matmul_prepacked(x, pre, kernel="gemv")
+    ll = torch.zeros(2, 16, N, dtype=torch.int32, device=dev)
+    ctl = torch.zeros(2, dtype=torch.int32, device=dev)
+    ptrs = (ctypes.c_void_p * 1)(ll.data_ptr())
+    out = torch.empty(M, N, dtype=torch.float16, device=dev)
+
+    def call():
+        rc = lib.q4b_gemv_exchange_dev(x.data_ptr(), _cabi.F16, M, K, pre.data.data_ptr(), K, N, ptrs, 1, 0, N, ll.data_ptr(), 16 * N, 1,
+                                       ctl.data_ptr(), out.data_ptr(), N, 0, _cabi.stream_ptr(dev))
+        assert rc == 0
+
+    for i in range(5):
+        out.zero_()
+        call()
+        assert torch.equal(out, ref)
+        assert ctl.tolist() == [i + 1, 0]
+        assert int(ll.abs().sum().item()) == 0                 # every word that was read is cleared again
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            call()
+        for _ in range(4):
+            out.zero_()
+            graph.replay()
+    side.synchronize()
+    assert torch.equal(out, ref) and ctl.tolist()[0] == 5 + 4 and Q.wait_status(dev) == 0
