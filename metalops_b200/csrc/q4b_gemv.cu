@@ -745,7 +745,10 @@ static int launch_gemv_ks(int ksplit, const void *x, int M, int64_t ldx, const v
 // Reader side of the self-validating words: every thread polls its words until they carry this call's tag
 // (bounded: code 700 and zeros on giving up), then writes the plain values.  SLOTS > 1: the row holds SLOTS
 // partial results side by side (one per rank), summed here in fp32 in slot order and rounded once.
-constexpr long long LL_WAIT_CYCLES = 1LL << 29;      // ~0.3 s
+// A peer may be late for reasons that have nothing to do with the GPU (a host thread that was descheduled, a
+// first call that still loads its module), so this bound is seconds, not the fraction of a second of the
+// waits inside one kernel.
+constexpr long long LL_WAIT_CYCLES = 1LL << 32;      // ~2.3 s
 // ctl != null: ctl[0] is the call counter (see PeerOut), ctl[1] counts the blocks that are done; the words
 // read are set back to 0 (no epoch), so nothing stale survives a call, and the last block out bumps ctl[0].
 template <bool BF16, bool SUM>

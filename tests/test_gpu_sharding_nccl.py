@@ -169,7 +169,7 @@ def test_barrier_free_gather_on_one_gpu(M, dtype):
         assert lib.q4b_gather_ll_unpack(lls[0].data_ptr(), M, N // 2, N, 2, epoch, code, summed.data_ptr(), N // 2, sp) == 0
         assert torch.equal(summed, (locals_[0].float() + locals_[1].float()).to(dtype))
     assert Q.wait_status(dev) == 0
-    # nobody stores epoch 7: the wait gives up after a fraction of a second
+    # nobody stores epoch 7: the wait gives up after about two seconds
     out = torch.full((M, N), 3.0, dtype=dtype, device=dev)
     assert lib.q4b_gather_ll_unpack(lls[0].data_ptr(), M, 64, N, 1, 7, code, out.data_ptr(), N, sp) == 0
     detail = ctypes.c_int(0)
